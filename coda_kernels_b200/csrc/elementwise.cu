@@ -1,0 +1,402 @@
+// HBM-bound side kernels of the fused-linear operators: the activation
+// gradients that feed the backward GEMMs, the log-sum-exp reduction and the
+// in-place softmax-gradient pass.  All of them move 16 bytes per thread per
+// access and keep their math in fp32.  See include/coda_b200.h for the contract.
+#include "../../include/coda_b200.h"
+#include "gemm_host.cuh"
+
+using namespace cb;
+
+namespace {
+
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+inline int launch_check(const char* what) {
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return fail(kCudaError, std::string(what) + ": " + cudaGetErrorString(e));
+  return kOk;
+}
+
+// ------------------------------------------------------------------ dSwiGLU
+// One thread: 8 outputs of dout <-> 16 interleaved (gate, up) values.
+__global__ void __launch_bounds__(256) dswiglu_kernel(const __nv_bfloat16* __restrict__ preact, long long ld_pre,
+                                                      const __nv_bfloat16* __restrict__ dout, long long ld_dout,
+                                                      __nv_bfloat16* __restrict__ grad, long long ld_grad, int M, int F8) {
+  const long long total = static_cast<long long>(M) * F8;
+  for (long long idx = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; idx < total;
+       idx += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const int row = static_cast<int>(idx / F8);
+    const int g8 = static_cast<int>(idx - static_cast<long long>(row) * F8);
+    const uint4 d4 = *reinterpret_cast<const uint4*>(dout + row * ld_dout + g8 * 8);
+    const uint4* zp = reinterpret_cast<const uint4*>(preact + row * ld_pre + g8 * 16);
+    const uint4 z0 = zp[0], z1 = zp[1];
+    const uint32_t dw[4] = {d4.x, d4.y, d4.z, d4.w};
+    const uint32_t zw[8] = {z0.x, z0.y, z0.z, z0.w, z1.x, z1.y, z1.z, z1.w};
+    uint32_t ow[8];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float2 dd = unpack_bf16x2(dw[j]);
+      const float t[2] = {dd.x, dd.y};
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        const float2 gu = unpack_bf16x2(zw[2 * j + h]);
+        const float g = gu.x, u = gu.y;
+        const float s = fast_sigmoid(g);
+        const float dg = t[h] * u * (s + g * s * (1.0f - s));
+        const float du = t[h] * g * s;
+        ow[2 * j + h] = pack_bf16x2(dg, du);
+      }
+    }
+    uint4* op = reinterpret_cast<uint4*>(grad + row * ld_grad + g8 * 16);
+    op[0] = make_uint4(ow[0], ow[1], ow[2], ow[3]);
+    op[1] = make_uint4(ow[4], ow[5], ow[6], ow[7]);
+  }
+}
+
+// ------------------------------------------------------------------ dSigmoid
+template <typename OutT>
+__global__ void __launch_bounds__(256) dsigmoid_kernel(const OutT* __restrict__ out, long long ld_out,
+                                                       const __nv_bfloat16* __restrict__ dout, long long ld_dout,
+                                                       __nv_bfloat16* __restrict__ grad, long long ld_grad, int M, int N8) {
+  const long long total = static_cast<long long>(M) * N8;
+  for (long long idx = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; idx < total;
+       idx += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const int row = static_cast<int>(idx / N8);
+    const int c8 = static_cast<int>(idx - static_cast<long long>(row) * N8);
+    const uint4 d4 = *reinterpret_cast<const uint4*>(dout + row * ld_dout + c8 * 8);
+    const uint32_t dw[4] = {d4.x, d4.y, d4.z, d4.w};
+    float o[8];
+    if constexpr (sizeof(OutT) == 2) {
+      const uint4 o4 = *reinterpret_cast<const uint4*>(out + row * ld_out + c8 * 8);
+      const uint32_t w[4] = {o4.x, o4.y, o4.z, o4.w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 f = unpack_bf16x2(w[j]);
+        o[2 * j] = f.x;
+        o[2 * j + 1] = f.y;
+      }
+    } else {
+      const float4* p = reinterpret_cast<const float4*>(out + row * ld_out + c8 * 8);
+      const float4 a = p[0], b = p[1];
+      o[0] = a.x; o[1] = a.y; o[2] = a.z; o[3] = a.w;
+      o[4] = b.x; o[5] = b.y; o[6] = b.z; o[7] = b.w;
+    }
+    uint32_t r[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float2 dd = unpack_bf16x2(dw[j]);
+      r[j] = pack_bf16x2(dd.x * o[2 * j] * (1.0f - o[2 * j]), dd.y * o[2 * j + 1] * (1.0f - o[2 * j + 1]));
+    }
+    *reinterpret_cast<uint4*>(grad + row * ld_grad + c8 * 8) = make_uint4(r[0], r[1], r[2], r[3]);
+  }
+}
+
+// ------------------------------------------------------------------ LSE finalize: one warp per row
+__global__ void __launch_bounds__(256) lse_finalize_kernel(const float* __restrict__ part_max, const float* __restrict__ part_sum,
+                                                           int tiles_n, const int* __restrict__ target,
+                                                           const float* __restrict__ target_logit, int ignore_index,
+                                                           float* __restrict__ lse, float* __restrict__ losses, int M) {
+  const int lane = threadIdx.x & 31;
+  const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (row >= M) return;
+  const float* pm = part_max + static_cast<long long>(row) * tiles_n;
+  const float* ps = part_sum + static_cast<long long>(row) * tiles_n;
+  float mx = -INFINITY;
+  for (int t = lane; t < tiles_n; t += 32) mx = fmaxf(mx, pm[t]);
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+  float s = 0.f;
+  for (int t = lane; t < tiles_n; t += 32) s += ps[t] * __expf(pm[t] - mx);
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+  if (lane == 0) {
+    const float l = mx + logf(s);
+    lse[row] = l;
+    losses[row] = (target[row] != ignore_index) ? (l - target_logit[row]) : 0.0f;
+  }
+}
+
+// ------------------------------------------------------------------ softmax-gradient fix-up, in place
+__global__ void __launch_bounds__(256) ce_grad_fixup_kernel(__nv_bfloat16* __restrict__ P, long long ldp,
+                                                            const float* __restrict__ part_max, int tiles_n, int tile_w,
+                                                            const float* __restrict__ lse, const int* __restrict__ target,
+                                                            int ignore_index, int N8) {
+  const int row = blockIdx.y;
+  const int c8 = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c8 >= N8) return;
+  const int col = c8 * 8;
+  uint4* ptr = reinterpret_cast<uint4*>(P + row * ldp + col);
+  const int tgt = target[row];
+  if (tgt == ignore_index) {
+    *ptr = make_uint4(0u, 0u, 0u, 0u);
+    return;
+  }
+  const float f = __expf(part_max[static_cast<long long>(row) * tiles_n + col / tile_w] - lse[row]);
+  const uint4 p4 = *ptr;
+  const uint32_t w[4] = {p4.x, p4.y, p4.z, p4.w};
+  uint32_t r[4];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    float2 v = unpack_bf16x2(w[j]);
+    v.x = v.x * f - ((col + 2 * j) == tgt ? 1.0f : 0.0f);
+    v.y = v.y * f - ((col + 2 * j + 1) == tgt ? 1.0f : 0.0f);
+    r[j] = pack_bf16x2(v.x, v.y);
+  }
+  *ptr = make_uint4(r[0], r[1], r[2], r[3]);
+}
+
+// ------------------------------------------------------------------ QK-norm + RoPE backward
+constexpr int kQkRowsPerBlock = 16;
+constexpr int kQkWarps = 8;
+
+// One warp per (row, head): un-rotate dy, take the RMSNorm VJP at the saved
+// statistic, accumulate the gamma gradient in registers; at the end the block
+// folds its warps and writes one partial row of [gamma_q | gamma_k] sums.
+template <int kHD>
+__global__ void __launch_bounds__(kQkWarps * 32)
+qknorm_rope_bwd_kernel(const __nv_bfloat16* __restrict__ dq, long long ld_dq, const __nv_bfloat16* __restrict__ dk,
+                       long long ld_dk, const __nv_bfloat16* __restrict__ dv, long long ld_dv, int nv8,
+                       const __nv_bfloat16* __restrict__ preact, long long ld_pre, const float* __restrict__ mean_sq,
+                       const __nv_bfloat16* __restrict__ gamma, const void* __restrict__ positions, int pos_is_float,
+                       const float* __restrict__ freq, int hq, int hk, float eps, __nv_bfloat16* __restrict__ grad,
+                       long long ld_grad, float* __restrict__ partials, int M) {
+  constexpr int kE = kHD / 32;  // elements per lane (4 or 2)
+  constexpr float kTwoPi = 6.283185307179586f;
+  __shared__ float red[kQkWarps][2 * kHD];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int heads = hq + hk;
+  const int row0 = blockIdx.x * kQkRowsPerBlock;
+  const int nrows = min(kQkRowsPerBlock, M - row0);
+  const int e0 = lane * kE;
+
+  float gq[kE], gk[kE], gam_q[kE], gam_k[kE];
+#pragma unroll
+  for (int j = 0; j < kE; ++j) {
+    gq[j] = 0.f;
+    gk[j] = 0.f;
+    gam_q[j] = __bfloat162float(gamma[e0 + j]);
+    gam_k[j] = __bfloat162float(gamma[kHD + e0 + j]);
+  }
+
+  const int items = nrows * heads;
+  for (int it = warp; it < items; it += kQkWarps) {
+    const int r_local = it / heads;
+    const int head = it - r_local * heads;
+    const int row = row0 + r_local;
+    const bool is_q = head < hq;
+    const __nv_bfloat16* dy_p = is_q ? dq + row * ld_dq + head * kHD + e0 : dk + row * ld_dk + (head - hq) * kHD + e0;
+    const __nv_bfloat16* x_p = preact + row * ld_pre + head * kHD + e0;
+    const float* f_p = freq + head * kHD + e0;
+    const float pos = pos_is_float ? reinterpret_cast<const float*>(positions)[row]
+                                   : static_cast<float>(reinterpret_cast<const int*>(positions)[row]);
+    float dy[kE], xh[kE], fr[kE];
+    if constexpr (kE == 4) {
+      const uint2 a = *reinterpret_cast<const uint2*>(dy_p);
+      const uint2 b = *reinterpret_cast<const uint2*>(x_p);
+      const float4 f = *reinterpret_cast<const float4*>(f_p);
+      float2 t;
+      t = unpack_bf16x2(a.x); dy[0] = t.x; dy[1] = t.y;
+      t = unpack_bf16x2(a.y); dy[2] = t.x; dy[3] = t.y;
+      t = unpack_bf16x2(b.x); xh[0] = t.x; xh[1] = t.y;
+      t = unpack_bf16x2(b.y); xh[2] = t.x; xh[3] = t.y;
+      fr[0] = f.x; fr[1] = f.y; fr[2] = f.z; fr[3] = f.w;
+    } else {
+      const uint32_t a = *reinterpret_cast<const uint32_t*>(dy_p);
+      const uint32_t b = *reinterpret_cast<const uint32_t*>(x_p);
+      const float2 f = *reinterpret_cast<const float2*>(f_p);
+      float2 t;
+      t = unpack_bf16x2(a); dy[0] = t.x; dy[1] = t.y;
+      t = unpack_bf16x2(b); xh[0] = t.x; xh[1] = t.y;
+      fr[0] = f.x; fr[1] = f.y;
+    }
+    const float ms = mean_sq[static_cast<long long>(row) * heads + head];
+    const float r = rsqrtf(ms + eps);
+    float dz[kE];
+    float dot = 0.f;
+#pragma unroll
+    for (int p = 0; p < kE / 2; ++p) {
+      const float hi = fr[2 * p], lo = fr[2 * p + 1];
+      const float t = pos * hi;
+      const float terr = fmaf(pos, hi, -t);
+      const float l = fmaf(pos, lo, terr);
+      const float frac = (t - rintf(t)) + l;
+      float sn, cs;
+      __sincosf(kTwoPi * frac, &sn, &cs);
+      const float a = dy[2 * p], b = dy[2 * p + 1];
+      dz[2 * p] = a * cs + b * sn;
+      dz[2 * p + 1] = b * cs - a * sn;
+    }
+#pragma unroll
+    for (int j = 0; j < kE; ++j) {
+      const float g = is_q ? gam_q[j] : gam_k[j];
+      dot = fmaf(dz[j] * g, xh[j], dot);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
+    const float coef = dot * r * r * r * (1.0f / kHD);
+    float out[kE];
+#pragma unroll
+    for (int j = 0; j < kE; ++j) {
+      const float g = is_q ? gam_q[j] : gam_k[j];
+      out[j] = r * g * dz[j] - xh[j] * coef;
+      const float dgj = dz[j] * xh[j] * r;
+      if (is_q) gq[j] += dgj;
+      else gk[j] += dgj;
+    }
+    __nv_bfloat16* o_p = grad + row * ld_grad + head * kHD + e0;
+    if constexpr (kE == 4) {
+      *reinterpret_cast<uint2*>(o_p) = make_uint2(pack_bf16x2(out[0], out[1]), pack_bf16x2(out[2], out[3]));
+    } else {
+      *reinterpret_cast<uint32_t*>(o_p) = pack_bf16x2(out[0], out[1]);
+    }
+  }
+
+  // copy dv next to grad_pre so that one GEMM consumes [grad_pre | dv]
+  if (dv != nullptr) {
+    const int total = nrows * nv8;
+    const long long col_off = static_cast<long long>(heads) * kHD;
+    for (int i = threadIdx.x; i < total; i += blockDim.x) {
+      const int r_local = i / nv8;
+      const int c8 = i - r_local * nv8;
+      const int row = row0 + r_local;
+      *reinterpret_cast<uint4*>(grad + row * ld_grad + col_off + c8 * 8) =
+          *reinterpret_cast<const uint4*>(dv + row * ld_dv + c8 * 8);
+    }
+  }
+
+#pragma unroll
+  for (int j = 0; j < kE; ++j) {
+    red[warp][e0 + j] = gq[j];
+    red[warp][kHD + e0 + j] = gk[j];
+  }
+  __syncthreads();
+  for (int c = threadIdx.x; c < 2 * kHD; c += blockDim.x) {
+    float s = 0.f;
+#pragma unroll
+    for (int w = 0; w < kQkWarps; ++w) s += red[w][c];
+    partials[static_cast<long long>(blockIdx.x) * (2 * kHD) + c] = s;
+  }
+}
+
+__global__ void __launch_bounds__(256) fold_partials_kernel(const float* __restrict__ partials, int nblocks, int width,
+                                                            float* __restrict__ out) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= width) return;
+  float s = 0.f;
+  for (int b = 0; b < nblocks; ++b) s += partials[static_cast<long long>(b) * width + c];
+  out[c] = s;
+}
+
+inline int grid_for(long long total, int block) {
+  long long g = (total + block - 1) / block;
+  const long long cap = static_cast<long long>(sm_count()) * 16;
+  if (g > cap) g = cap;
+  if (g < 1) g = 1;
+  return static_cast<int>(g);
+}
+
+}  // namespace
+
+extern "C" int coda_b200_dswiglu(const void* preact, int64_t ld_pre, const void* dout, int64_t ld_dout, void* grad_pre,
+                                 int64_t ld_grad, int M, int F, void* stream) {
+  if (!preact || !dout || !grad_pre) return fail(kBadArgument, "NULL pointer");
+  if (M <= 0 || F <= 0 || F % 8 != 0) return fail(kBadArgument, "F must be a positive multiple of 8");
+  if (ld_pre % 8 || ld_dout % 8 || ld_grad % 8 || ld_pre < 2 * F || ld_grad < 2 * F || ld_dout < F)
+    return fail(kBadArgument, "leading dimensions must be multiples of 8 and cover the row");
+  if (!aligned16(preact) || !aligned16(dout) || !aligned16(grad_pre)) return fail(kBadArgument, "pointers must be 16-byte aligned");
+  const int F8 = F / 8;
+  dswiglu_kernel<<<grid_for(static_cast<long long>(M) * F8, 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(preact), ld_pre, static_cast<const __nv_bfloat16*>(dout), ld_dout,
+      static_cast<__nv_bfloat16*>(grad_pre), ld_grad, M, F8);
+  return launch_check("dswiglu launch");
+}
+
+extern "C" int coda_b200_dsigmoid(const void* out, int64_t ld_out, int out_is_fp32, const void* dout, int64_t ld_dout,
+                                  void* grad_pre, int64_t ld_grad, int M, int N, void* stream) {
+  if (!out || !dout || !grad_pre) return fail(kBadArgument, "NULL pointer");
+  if (M <= 0 || N <= 0 || N % 8 != 0) return fail(kBadArgument, "N must be a positive multiple of 8");
+  if (ld_out % 8 || ld_dout % 8 || ld_grad % 8 || ld_out < N || ld_dout < N || ld_grad < N)
+    return fail(kBadArgument, "leading dimensions must be multiples of 8 and cover the row");
+  if (!aligned16(out) || !aligned16(dout) || !aligned16(grad_pre)) return fail(kBadArgument, "pointers must be 16-byte aligned");
+  const int N8 = N / 8;
+  const int grid = grid_for(static_cast<long long>(M) * N8, 256);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (out_is_fp32)
+    dsigmoid_kernel<float><<<grid, 256, 0, st>>>(static_cast<const float*>(out), ld_out, static_cast<const __nv_bfloat16*>(dout),
+                                                 ld_dout, static_cast<__nv_bfloat16*>(grad_pre), ld_grad, M, N8);
+  else
+    dsigmoid_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(out), ld_out,
+                                                         static_cast<const __nv_bfloat16*>(dout), ld_dout,
+                                                         static_cast<__nv_bfloat16*>(grad_pre), ld_grad, M, N8);
+  return launch_check("dsigmoid launch");
+}
+
+extern "C" int coda_b200_lse_finalize(const float* part_max, const float* part_sum, int tiles_n, const int32_t* target,
+                                      const float* target_logit, int ignore_index, float* lse, float* losses, int M,
+                                      void* stream) {
+  if (!part_max || !part_sum || !target || !target_logit || !lse || !losses) return fail(kBadArgument, "NULL pointer");
+  if (M <= 0 || tiles_n <= 0) return fail(kBadArgument, "M and tiles_n must be positive");
+  const int rows_per_block = 8;
+  lse_finalize_kernel<<<(M + rows_per_block - 1) / rows_per_block, rows_per_block * 32, 0, static_cast<cudaStream_t>(stream)>>>(
+      part_max, part_sum, tiles_n, target, target_logit, ignore_index, lse, losses, M);
+  return launch_check("lse_finalize launch");
+}
+
+extern "C" int coda_b200_ce_grad_fixup(void* P, int64_t ldp, const float* part_max, int tiles_n, const float* lse,
+                                       const int32_t* target, int ignore_index, int M, int N, void* stream) {
+  if (!P || !part_max || !lse || !target) return fail(kBadArgument, "NULL pointer");
+  if (M <= 0 || N <= 0 || N % 8 != 0 || ldp % 8 != 0 || ldp < N || !aligned16(P))
+    return fail(kBadArgument, "P must be 16-byte aligned, N and ldp multiples of 8");
+  if (M > 65535 * 64) return fail(kBadArgument, "M too large for the fix-up grid");
+  if (tiles_n != coda_b200_lse_tiles(N)) return fail(kBadArgument, "tiles_n does not match coda_b200_lse_tiles(N)");
+  const int N8 = N / 8;
+  dim3 grid((N8 + 255) / 256, M, 1);
+  if (M > 65535) return fail(kBadArgument, "M above 65535 is not supported by the fix-up grid");
+  ce_grad_fixup_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<__nv_bfloat16*>(P), ldp, part_max,
+                                                                           tiles_n, 256, lse, target, ignore_index, N8);
+  return launch_check("ce_grad_fixup launch");
+}
+
+extern "C" int64_t coda_b200_qknorm_rope_bwd_scratch_bytes(int M, int head_dim) {
+  const long long blocks = (static_cast<long long>(M) + kQkRowsPerBlock - 1) / kQkRowsPerBlock;
+  return blocks * 2 * head_dim * static_cast<long long>(sizeof(float));
+}
+
+extern "C" int coda_b200_qknorm_rope_bwd(const void* dq, int64_t ld_dq, const void* dk, int64_t ld_dk, const void* dv,
+                                         int64_t ld_dv, int nv, const void* preact, int64_t ld_pre, const float* mean_sq,
+                                         const void* gamma, const void* positions, int pos_is_float, const float* frequencies,
+                                         int head_dim, int hq, int hk, float eps, void* grad, int64_t ld_grad, float* dgamma,
+                                         void* scratch, int64_t scratch_bytes, int M, void* stream) {
+  if (!preact || !mean_sq || !gamma || !positions || !frequencies || !grad || !dgamma || !scratch)
+    return fail(kBadArgument, "NULL pointer");
+  if (head_dim != 64 && head_dim != 128) return fail(kBadArgument, "head_dim must be 64 or 128");
+  if (M <= 0 || hq < 0 || hk < 0 || hq + hk <= 0) return fail(kBadArgument, "bad extents");
+  if ((hq > 0 && !dq) || (hk > 0 && !dk)) return fail(kBadArgument, "dq / dk required");
+  if (scratch_bytes < coda_b200_qknorm_rope_bwd_scratch_bytes(M, head_dim)) return fail(kBadArgument, "scratch buffer too small");
+  // 8-byte vector accesses on dq / dk / preact / grad rows, 16-byte on dv and frequencies
+  if (ld_dq % 4 || ld_dk % 4 || ld_pre % 4 || ld_grad % 8) return fail(kBadArgument, "row strides must be multiples of 4 (grad: 8) elements");
+  if ((reinterpret_cast<uintptr_t>(dq) & 7u) || (reinterpret_cast<uintptr_t>(dk) & 7u) || (reinterpret_cast<uintptr_t>(preact) & 7u) ||
+      !aligned16(grad) || !aligned16(frequencies))
+    return fail(kBadArgument, "misaligned pointer");
+  if (dv != nullptr && (nv <= 0 || nv % 8 || ld_dv % 8 || !aligned16(dv))) return fail(kBadArgument, "bad dv extent / alignment");
+  const int blocks = (M + kQkRowsPerBlock - 1) / kQkRowsPerBlock;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  float* partials = static_cast<float*>(scratch);
+  const int nv8 = dv ? nv / 8 : 0;
+  if (head_dim == 128)
+    qknorm_rope_bwd_kernel<128><<<blocks, kQkWarps * 32, 0, st>>>(
+        static_cast<const __nv_bfloat16*>(dq), ld_dq, static_cast<const __nv_bfloat16*>(dk), ld_dk,
+        static_cast<const __nv_bfloat16*>(dv), ld_dv, nv8, static_cast<const __nv_bfloat16*>(preact), ld_pre, mean_sq,
+        static_cast<const __nv_bfloat16*>(gamma), positions, pos_is_float, frequencies, hq, hk, eps,
+        static_cast<__nv_bfloat16*>(grad), ld_grad, partials, M);
+  else
+    qknorm_rope_bwd_kernel<64><<<blocks, kQkWarps * 32, 0, st>>>(
+        static_cast<const __nv_bfloat16*>(dq), ld_dq, static_cast<const __nv_bfloat16*>(dk), ld_dk,
+        static_cast<const __nv_bfloat16*>(dv), ld_dv, nv8, static_cast<const __nv_bfloat16*>(preact), ld_pre, mean_sq,
+        static_cast<const __nv_bfloat16*>(gamma), positions, pos_is_float, frequencies, hq, hk, eps,
+        static_cast<__nv_bfloat16*>(grad), ld_grad, partials, M);
+  int rc = launch_check("qknorm_rope_bwd launch");
+  if (rc != kOk) return rc;
+  fold_partials_kernel<<<(2 * head_dim + 255) / 256, 256, 0, st>>>(partials, blocks, 2 * head_dim, dgamma);
+  return launch_check("fold_partials launch");
+}

@@ -1,0 +1,300 @@
+// Fused epilogues for the tcgen05 GEMM core.  With the 32x32b TMEM load shape
+// every epilogue thread owns one accumulator row and reads runs of 32
+// consecutive fp32 columns, so gate/up pairs, whole attention heads and the
+// row-wise max / sum-exp of a tile are all thread-local: no shuffles needed.
+//
+// Each epilogue provides
+//   struct Params                         plain-old-data kernel argument
+//   static void prologue(p, scratch, tid) once per CTA, before the role split
+//   template <int kBN> static void run(p, ctx, scratch)   once per tile per epilogue thread
+#pragma once
+
+#include "gemm_core.cuh"
+
+namespace cb {
+
+// Store 32 consecutive values of one row, 16 bytes at a time, predicated on the
+// column tail.  `ncols` = number of valid columns starting at v[0] (a multiple of 8).
+__device__ __forceinline__ void store_row32(__nv_bfloat16* dst, const float* v, int ncols) {
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    if (j * 8 < ncols) {
+      uint4 u;
+      u.x = pack_bf16x2(v[j * 8 + 0], v[j * 8 + 1]);
+      u.y = pack_bf16x2(v[j * 8 + 2], v[j * 8 + 3]);
+      u.z = pack_bf16x2(v[j * 8 + 4], v[j * 8 + 5]);
+      u.w = pack_bf16x2(v[j * 8 + 6], v[j * 8 + 7]);
+      *reinterpret_cast<uint4*>(dst + j * 8) = u;
+    }
+  }
+}
+__device__ __forceinline__ void store_row32(float* dst, const float* v, int ncols) {
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    if (j * 4 < ncols) {
+      *reinterpret_cast<float4*>(dst + j * 4) = make_float4(v[j * 4], v[j * 4 + 1], v[j * 4 + 2], v[j * 4 + 3]);
+    }
+  }
+}
+
+// ------------------------------------------------------------------ plain / sigmoid
+// D = act(alpha * acc).  Replaces the reference's `_gemm`, `_gemm_scalar_scale_epi`
+// and `_gemm_sigmoid_epi` (coda/core/gemm/functional.py:35-51, 94-113, 199-217).
+enum class Act { kNone, kSigmoid };
+
+template <typename OutT, Act kAct>
+struct EpiStore {
+  struct Params {
+    OutT* D;
+    long long ldd;
+    const float* alpha;  // device scalar or nullptr (= 1)
+  };
+  __device__ static void prologue(const Params&, uint8_t*, int) {}
+
+  template <int kBN>
+  __device__ static void run(const Params& p, const EpiCtx& c, uint8_t*) {
+    const float alpha = p.alpha ? __ldg(p.alpha) : 1.0f;
+    const bool row_ok = c.row < c.M;
+    OutT* drow = p.D + static_cast<long long>(c.row) * p.ldd + c.n0;
+#pragma unroll 1
+    for (int ch = 0; ch < kBN / 32; ++ch) {
+      const int col = c.n0 + ch * 32;
+      if (col >= c.N) break;  // warp-uniform
+      float v[32];
+      tmem_ld32(c.taddr + ch * 32, v);
+      tmem_ld_wait();
+#pragma unroll
+      for (int j = 0; j < 32; ++j) {
+        float x = v[j] * alpha;
+        if constexpr (kAct == Act::kSigmoid) x = fast_sigmoid(x);
+        v[j] = x;
+      }
+      if (row_ok) store_row32(drow + ch * 32, v, c.N - col);
+    }
+  }
+};
+
+// ------------------------------------------------------------------ SwiGLU
+// preact[:, c] = bf16(acc[:, c]); postact[:, j] = bf16(silu(acc[:, 2j]) * acc[:, 2j+1]),
+// both from the unrounded accumulator.  Replaces `_gemm_swiglu_epi`
+// (coda/core/gemm/functional.py:237-258, epilogue coda/core/gemm/epilogues.py:44-47).
+struct EpiSwiGLU {
+  struct Params {
+    __nv_bfloat16* preact;  // [M, N]
+    long long ld_pre;
+    __nv_bfloat16* postact;  // [M, N/2]
+    long long ld_post;
+  };
+  __device__ static void prologue(const Params&, uint8_t*, int) {}
+
+  template <int kBN>
+  __device__ static void run(const Params& p, const EpiCtx& c, uint8_t*) {
+    const bool row_ok = c.row < c.M;
+    __nv_bfloat16* pre = p.preact + static_cast<long long>(c.row) * p.ld_pre + c.n0;
+    __nv_bfloat16* post = p.postact + static_cast<long long>(c.row) * p.ld_post + c.n0 / 2;
+#pragma unroll 1
+    for (int ch = 0; ch < kBN / 32; ++ch) {
+      const int col = c.n0 + ch * 32;
+      if (col >= c.N) break;
+      float v[32];
+      tmem_ld32(c.taddr + ch * 32, v);
+      tmem_ld_wait();
+      float o[16];
+#pragma unroll
+      for (int j = 0; j < 16; ++j) {
+        const float g = v[2 * j], u = v[2 * j + 1];
+        o[j] = g * fast_sigmoid(g) * u;
+      }
+      if (row_ok) {
+        const int ncols = c.N - col;
+        store_row32(pre + ch * 32, v, ncols);
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+          if (j * 16 < ncols) {  // N is a multiple of 16 for this op, so half-chunks are all-or-nothing
+            uint4 u4;
+            u4.x = pack_bf16x2(o[j * 8 + 0], o[j * 8 + 1]);
+            u4.y = pack_bf16x2(o[j * 8 + 2], o[j * 8 + 3]);
+            u4.z = pack_bf16x2(o[j * 8 + 4], o[j * 8 + 5]);
+            u4.w = pack_bf16x2(o[j * 8 + 6], o[j * 8 + 7]);
+            *reinterpret_cast<uint4*>(post + ch * 16 + j * 8) = u4;
+          }
+        }
+      }
+    }
+  }
+};
+
+// ------------------------------------------------------------------ log-sum-exp partials (+ optional probability store)
+// Per (row, column-tile): m = max_j acc, s = sum_j exp(acc - m).  The tile that
+// contains the row's target column also records that logit (fp32, unrounded).
+// With kStoreP the tile's unnormalised probabilities exp(acc - m) are stored in
+// bf16 so that the backward never needs the logits; a later in-place pass
+// rescales them by exp(m - lse) and subtracts the one-hot.  Replaces
+// `_gemm_lse_epi` / `_lse_select_logits_epi` (coda/core/gemm/functional.py:342-368, 453-493).
+template <bool kStoreP>
+struct EpiLse {
+  struct Params {
+    __nv_bfloat16* P;  // [M, N] or nullptr
+    long long ldp;
+    float* part_max;  // [M, tiles_n]
+    float* part_sum;  // [M, tiles_n]
+    int tiles_n;
+    const int* target;    // [M]
+    float* target_logit;  // [M]; written only by the tile holding the target column
+  };
+  __device__ static void prologue(const Params&, uint8_t*, int) {}
+
+  template <int kBN>
+  __device__ static void run(const Params& p, const EpiCtx& c, uint8_t*) {
+    const bool row_ok = c.row < c.M;
+    const int nvalid = min(kBN, c.N - c.n0);  // valid columns in this tile (>= 1)
+    constexpr float kLog2e = 1.4426950408889634f;
+    // pass 1: row maximum over the tile
+    float mx = -INFINITY;
+#pragma unroll 1
+    for (int ch = 0; ch < kBN / 32; ++ch) {
+      if (ch * 32 >= nvalid) break;
+      float v[32];
+      tmem_ld32(c.taddr + ch * 32, v);
+      tmem_ld_wait();
+      const int lim = nvalid - ch * 32;
+#pragma unroll
+      for (int j = 0; j < 32; ++j)
+        if (j < lim) mx = fmaxf(mx, v[j]);
+    }
+    // pass 2: exponentials, their sum, target logit, optional store
+    const int tgt = row_ok ? __ldg(p.target + c.row) : -1;
+    const int tcol = tgt - c.n0;  // target column relative to this tile
+    float sum = 0.f, tlogit = 0.f;
+    __nv_bfloat16* prow = kStoreP ? p.P + static_cast<long long>(c.row) * p.ldp + c.n0 : nullptr;
+    const float mxs = mx * kLog2e;
+#pragma unroll 1
+    for (int ch = 0; ch < kBN / 32; ++ch) {
+      if (ch * 32 >= nvalid) break;
+      float v[32];
+      tmem_ld32(c.taddr + ch * 32, v);
+      tmem_ld_wait();
+      const int lim = nvalid - ch * 32;
+      const int trel = tcol - ch * 32;
+      if (trel >= 0 && trel < 32) {
+#pragma unroll
+        for (int j = 0; j < 32; ++j)
+          if (j == trel) tlogit = v[j];
+      }
+#pragma unroll
+      for (int j = 0; j < 32; ++j) {
+        const float e = (j < lim) ? fast_exp2(fmaf(v[j], kLog2e, -mxs)) : 0.f;
+        sum += e;
+        v[j] = e;
+      }
+      if (kStoreP && row_ok) store_row32(prow + ch * 32, v, lim);
+    }
+    if (row_ok) {
+      p.part_max[static_cast<long long>(c.row) * p.tiles_n + c.tn] = mx;
+      p.part_sum[static_cast<long long>(c.row) * p.tiles_n + c.tn] = sum;
+      if (tcol >= 0 && tcol < nvalid) p.target_logit[c.row] = tlogit;
+    }
+  }
+};
+
+// ------------------------------------------------------------------ per-head RMSNorm + RoPE on q,k; plain store for v
+// Columns are [q heads | k heads | v heads], each head kHD wide.  For q and k:
+//   ms = mean(acc^2) over the head (fp32, unrounded acc), r = rsqrt(ms + eps)
+//   y  = acc * gamma * r;  (y0, y1) at columns (2p, 2p+1) rotated by the angle
+//   2*pi*frac(pos * (hi + lo)) with (hi, lo) = frequencies[2p], frequencies[2p+1]
+//   evaluated with the two-term product so that large positions stay accurate.
+// Outputs: rotated qk, bf16 preact, ms; v columns are stored unchanged.
+// Replaces `_gemm_qknorm_rope_epi` + the separate v GEMM
+// (coda/core/gemm/functional.py:1079-1152, coda/core/gemm/epilogues.py:232-259,
+// angle scheme coda/core/ops/math_utils.py:181-195).
+template <int kHD>
+struct EpiQKNormRope {
+  struct Params {
+    __nv_bfloat16* qk;  // [M, size_qk]
+    long long ld_qk;
+    __nv_bfloat16* preact;  // [M, size_qk]
+    long long ld_pre;
+    __nv_bfloat16* v;  // [M, size_v] or nullptr when N == size_qk
+    long long ld_v;
+    float* mean_sq;              // [M, hq + hk]
+    const __nv_bfloat16* gamma;  // [2 * kHD] = [gamma_q | gamma_k]
+    const void* positions;       // [M] int32 or fp32
+    int pos_is_float;
+    const float* freq;  // [(hq + hk) * kHD] interleaved (hi, lo)
+    int hq, hk;
+    float eps;
+  };
+  __device__ static void prologue(const Params&, uint8_t*, int) {}
+
+  template <int kBN>
+  __device__ static void run(const Params& p, const EpiCtx& c, uint8_t*) {
+    const bool row_ok = c.row < c.M;
+    const int safe_row = row_ok ? c.row : 0;
+    const float pos = p.pos_is_float ? __ldg(reinterpret_cast<const float*>(p.positions) + safe_row)
+                                     : static_cast<float>(__ldg(reinterpret_cast<const int*>(p.positions) + safe_row));
+    const int nheads_qk = p.hq + p.hk;
+    constexpr float kTwoPi = 6.283185307179586f;
+#pragma unroll 1
+    for (int h = 0; h < kBN / kHD; ++h) {
+      const int col0 = c.n0 + h * kHD;
+      if (col0 >= c.N) break;
+      const int head = col0 / kHD;
+      const uint32_t t0 = c.taddr + h * kHD;
+      if (head >= nheads_qk) {
+        // v head: plain bf16 store
+        __nv_bfloat16* vrow = p.v + static_cast<long long>(c.row) * p.ld_v + (col0 - nheads_qk * kHD);
+#pragma unroll 1
+        for (int ch = 0; ch < kHD / 32; ++ch) {
+          float v[32];
+          tmem_ld32(t0 + ch * 32, v);
+          tmem_ld_wait();
+          if (row_ok) store_row32(vrow + ch * 32, v, 32);
+        }
+        continue;
+      }
+      // pass 1: mean square of the head
+      float ss = 0.f;
+#pragma unroll 1
+      for (int ch = 0; ch < kHD / 32; ++ch) {
+        float v[32];
+        tmem_ld32(t0 + ch * 32, v);
+        tmem_ld_wait();
+#pragma unroll
+        for (int j = 0; j < 32; ++j) ss = fmaf(v[j], v[j], ss);
+      }
+      const float ms = ss * (1.0f / kHD);
+      const float r = rsqrtf(ms + p.eps);
+      if (row_ok) p.mean_sq[static_cast<long long>(c.row) * nheads_qk + head] = ms;
+      const __nv_bfloat16* gam = p.gamma + (head < p.hq ? 0 : kHD);
+      __nv_bfloat16* prow = p.preact + static_cast<long long>(c.row) * p.ld_pre + col0;
+      __nv_bfloat16* orow = p.qk + static_cast<long long>(c.row) * p.ld_qk + col0;
+      // pass 2: normalise, rotate, store
+#pragma unroll 1
+      for (int ch = 0; ch < kHD / 32; ++ch) {
+        float v[32];
+        tmem_ld32(t0 + ch * 32, v);
+        tmem_ld_wait();
+        if (row_ok) store_row32(prow + ch * 32, v, 32);
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          const int e = ch * 32 + 2 * j;  // element index inside the head
+          const float2 g = unpack_bf16x2(__ldg(reinterpret_cast<const unsigned int*>(gam + e)));
+          const float2 f = __ldg(reinterpret_cast<const float2*>(p.freq + col0 + e));
+          const float y0 = v[2 * j] * g.x * r;
+          const float y1 = v[2 * j + 1] * g.y * r;
+          const float t = pos * f.x;
+          const float terr = fmaf(pos, f.x, -t);
+          const float l = fmaf(pos, f.y, terr);
+          const float frac = (t - rintf(t)) + l;
+          float sn, cs;
+          __sincosf(kTwoPi * frac, &sn, &cs);
+          v[2 * j] = y0 * cs - y1 * sn;
+          v[2 * j + 1] = y0 * sn + y1 * cs;
+        }
+        if (row_ok) store_row32(orow + ch * 32, v, 32);
+      }
+    }
+  }
+};
+
+}  // namespace cb

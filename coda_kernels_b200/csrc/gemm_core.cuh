@@ -1,0 +1,296 @@
+// Persistent, warp-specialised bf16 GEMM core for sm_100a.
+//
+//   D[M, N] = epilogue( A[M, K] * B[N, K]^T ),  fp32 accumulation in tensor memory.
+//
+// Roles inside one CTA of 192 threads:
+//   warp 0      TMA producer   global -> 128-byte-swizzled shared-memory ring (one elected lane)
+//   warp 1      MMA issuer     tcgen05.mma, accumulators in TMEM (one elected lane); owns TMEM alloc/dealloc
+//   warps 2..5  epilogue       tcgen05.ld TMEM -> registers -> fused math -> global stores
+//
+// Two accumulator stages live in TMEM so the epilogue of tile i overlaps the
+// mainloop of tile i+1.  With kCtaGroup == 2 two CTAs (a cluster of 2) share one
+// 256 x kBN tile: each CTA loads its own 128 rows of A and its own half of B,
+// the leader CTA issues tcgen05.mma.cta_group::2, and each CTA drains its own
+// 128 accumulator rows.  No multicast loads are used anywhere.
+//
+// A and B may each be K-major (contraction index contiguous) or MN-major
+// (row/column index contiguous); the transposed operands of the backward GEMMs
+// are consumed in place, without a physical transpose.
+#pragma once
+
+#include "ptx.cuh"
+
+namespace cb {
+
+constexpr int kBlockM = 128;  // accumulator rows per CTA (= TMEM lanes)
+constexpr int kBlockK = 64;   // bf16 elements per k-block = one 128-byte swizzle row
+constexpr int kUmmaK = 16;    // contraction depth of one tcgen05.mma (bf16)
+constexpr int kNumThreads = 192;
+constexpr int kNumEpiWarps = 4;
+constexpr int kSmemBudget = 227 * 1024;
+
+struct GemmShape {
+  int M, N, K;  // K = contraction length
+  int tiles_m;  // number of (kBlockM * kCtaGroup)-row tiles
+  int tiles_n;  // number of kBN-column tiles
+  int group_m;  // raster: tiles of `group_m` consecutive row-tiles share their column sweep (L2 reuse)
+  // Debug overrides for the MN-major descriptor offsets (0 = use the derived values).
+  int dbg_lbo_mn, dbg_sbo_mn;
+};
+
+// Per-thread view of one accumulator tile handed to an epilogue.
+struct EpiCtx {
+  int row;         // global row owned by this thread (may be >= M: loads still run, stores are predicated)
+  int n0;          // first global column of the tile
+  int tn;          // column-tile index
+  int M, N;        // problem extents
+  uint32_t taddr;  // TMEM address of (this warp's first lane, first column of the accumulator)
+  int lane;
+};
+
+template <int kCtaGroup, int kBN>
+struct GemmCfg {
+  static constexpr int kBNcta = kBN / kCtaGroup;  // B rows loaded by one CTA
+  static constexpr uint32_t kABytes = kBlockM * kBlockK * 2;
+  static constexpr uint32_t kBBytes = kBNcta * kBlockK * 2;
+  static constexpr uint32_t kStageBytes = kABytes + kBBytes;
+  static constexpr uint32_t kCtrlBytes = 1024;  // barriers, TMEM pointer, abort word
+  static constexpr uint32_t kEpiScratch = 2048;
+  static constexpr int kStagesFit = (kSmemBudget - 1024 - kCtrlBytes - kEpiScratch) / kStageBytes;
+  static constexpr int kStages = kStagesFit > 8 ? 8 : kStagesFit;
+  static constexpr uint32_t kSmemBytes = 1024 + kStages * kStageBytes + kCtrlBytes + kEpiScratch;
+  static constexpr uint32_t kTmemCols = 2 * kBN;  // two accumulator stages
+  static_assert(kBN == 128 || kBN == 256, "tile width must be 128 or 256");
+  static_assert(kStages >= 2, "need at least two pipeline stages");
+};
+
+__device__ __forceinline__ void tile_coords(const GemmShape& s, int tile, int& tm, int& tn) {
+  const int per_group = s.group_m * s.tiles_n;
+  const int g = tile / per_group;
+  const int first_m = g * s.group_m;
+  const int gsz = min(s.group_m, s.tiles_m - first_m);
+  const int r = tile - g * per_group;
+  tm = first_m + r % gsz;
+  tn = r / gsz;
+}
+
+template <int kCtaGroup, int kBN, bool kAMn, bool kBMn, class Epi>
+__global__ void __launch_bounds__(kNumThreads, 1)
+gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b, const GemmShape shape,
+            const typename Epi::Params ep, int* __restrict__ status) {
+  using Cfg = GemmCfg<kCtaGroup, kBN>;
+  constexpr int kStages = Cfg::kStages;
+  constexpr int kBNcta = Cfg::kBNcta;
+  constexpr uint32_t kABytes = Cfg::kABytes;
+  constexpr uint32_t kStageBytes = Cfg::kStageBytes;
+
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw_addr = smem_u32(smem_raw);
+  const uint32_t smem_base = (raw_addr + 1023u) & ~1023u;  // swizzle atoms need 1024-byte alignment
+  uint8_t* smem_gen = smem_raw + (smem_base - raw_addr);
+
+  const uint32_t ctrl = smem_base + kStages * kStageBytes;
+  const uint32_t bar_full = ctrl;                        // [kStages]
+  const uint32_t bar_empty = ctrl + 8 * kStages;         // [kStages]
+  const uint32_t bar_acc_full = ctrl + 16 * kStages;     // [2]
+  const uint32_t bar_acc_empty = bar_acc_full + 16;      // [2]
+  const uint32_t tmem_slot = bar_acc_empty + 16;         // uint32
+  volatile int* abort_word = reinterpret_cast<volatile int*>(smem_gen + kStages * kStageBytes + 16 * kStages + 40);
+  volatile uint32_t* tmem_slot_gen = reinterpret_cast<volatile uint32_t*>(smem_gen + kStages * kStageBytes + 16 * kStages + 32);
+  uint8_t* epi_scratch = smem_gen + kStages * kStageBytes + Cfg::kCtrlBytes;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t rank = (kCtaGroup == 2) ? cluster_ctarank() : 0u;
+  const bool leader = (rank == 0);
+  const int cluster_id = blockIdx.x / kCtaGroup;
+  const int num_clusters = gridDim.x / kCtaGroup;
+  const int num_tiles = shape.tiles_m * shape.tiles_n;
+  const int num_kb = (shape.K + kBlockK - 1) / kBlockK;
+
+  // ---------------------------------------------------------------- setup
+  if (warp == 0 && lane == 0) {
+    prefetch_tmap(&tmap_a);
+    prefetch_tmap(&tmap_b);
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(bar_full + 8 * s, 1);
+      mbar_init(bar_empty + 8 * s, 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(bar_acc_full + 8 * a, 1);
+      mbar_init(bar_acc_empty + 8 * a, kNumEpiWarps * kCtaGroup);
+    }
+    *abort_word = 0;
+    fence_barrier_init();
+  }
+  if (warp == 1) {
+    tmem_alloc<kCtaGroup>(tmem_slot, Cfg::kTmemCols);
+    tmem_relinquish<kCtaGroup>();
+  }
+  Epi::prologue(ep, epi_scratch, threadIdx.x);
+  tc_fence_before();
+  __syncthreads();
+  if constexpr (kCtaGroup == 2) {
+    cluster_arrive();
+    cluster_wait();
+  }
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot_gen;
+
+  if (warp == 0) {
+    // ============================================================ TMA producer
+    if (lane == 0) {
+      const uint32_t full_sig = (kCtaGroup == 2) ? mapa(bar_full, 0) : bar_full;  // the leader's barriers
+      uint32_t s = 0, ph = 0;
+      bool ok = true;
+      for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters) {
+        int tm, tn;
+        tile_coords(shape, tile, tm, tn);
+        const int a_row0 = tm * (kBlockM * kCtaGroup) + static_cast<int>(rank) * kBlockM;
+        const int b_row0 = tn * kBN + static_cast<int>(rank) * kBNcta;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(bar_empty + 8 * s, ph ^ 1u, abort_word, kErrTimeoutEmpty)) {
+            ok = false;
+            break;
+          }
+          if (leader) mbar_arrive_expect_tx(bar_full + 8 * s, kStageBytes * kCtaGroup);
+          const uint32_t a_dst = smem_base + s * kStageBytes;
+          const uint32_t b_dst = a_dst + kABytes;
+          const uint32_t sig = full_sig + 8 * s;
+          const int k0 = kb * kBlockK;
+          if constexpr (!kAMn) {
+            if constexpr (kCtaGroup == 2) tma_load_2d_pair(a_dst, &tmap_a, sig, k0, a_row0);
+            else tma_load_2d(a_dst, &tmap_a, sig, k0, a_row0);
+          } else {
+#pragma unroll
+            for (int j = 0; j < kBlockM / 64; ++j) {
+              if constexpr (kCtaGroup == 2) tma_load_2d_pair(a_dst + j * (kBlockK * 128), &tmap_a, sig, a_row0 + 64 * j, k0);
+              else tma_load_2d(a_dst + j * (kBlockK * 128), &tmap_a, sig, a_row0 + 64 * j, k0);
+            }
+          }
+          if constexpr (!kBMn) {
+            if constexpr (kCtaGroup == 2) tma_load_2d_pair(b_dst, &tmap_b, sig, k0, b_row0);
+            else tma_load_2d(b_dst, &tmap_b, sig, k0, b_row0);
+          } else {
+#pragma unroll
+            for (int j = 0; j < kBNcta / 64; ++j) {
+              if constexpr (kCtaGroup == 2) tma_load_2d_pair(b_dst + j * (kBlockK * 128), &tmap_b, sig, b_row0 + 64 * j, k0);
+              else tma_load_2d(b_dst + j * (kBlockK * 128), &tmap_b, sig, b_row0 + 64 * j, k0);
+            }
+          }
+          if (++s == kStages) {
+            s = 0;
+            ph ^= 1u;
+          }
+        }
+      }
+      // Tail: do not leave while commit-arrives for the last stages may still be
+      // on their way to this CTA's barriers.
+      for (int i = 0; i < kStages && ok; ++i) {
+        ok = mbar_wait(bar_empty + 8 * s, ph ^ 1u, abort_word, kErrTimeoutEmpty);
+        if (++s == kStages) {
+          s = 0;
+          ph ^= 1u;
+        }
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    // ============================================================ MMA issuer
+    if (leader && lane == 0) {
+      constexpr uint32_t idesc = make_idesc_bf16(kBlockM * kCtaGroup, kBN, kAMn, kBMn);
+      const uint32_t lbo_mn = shape.dbg_lbo_mn ? static_cast<uint32_t>(shape.dbg_lbo_mn) : static_cast<uint32_t>(kBlockK * 128);
+      const uint32_t sbo_mn = shape.dbg_sbo_mn ? static_cast<uint32_t>(shape.dbg_sbo_mn) : 1024u;
+      // K-major: 8-row groups 1024 B apart, one MMA step = 32 B along the swizzled row.
+      // MN-major: 64-element column blocks kBlockK*128 B apart, 8-k groups 1024 B apart, one MMA step = 2 groups.
+      const uint32_t a_lbo = kAMn ? lbo_mn : 16u, a_sbo = kAMn ? sbo_mn : 1024u, a_step = kAMn ? 2048u : 32u;
+      const uint32_t b_lbo = kBMn ? lbo_mn : 16u, b_sbo = kBMn ? sbo_mn : 1024u, b_step = kBMn ? 2048u : 32u;
+      uint32_t s = 0, ph = 0, it = 0;
+      bool ok = true;
+      for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters, ++it) {
+        const uint32_t acc = it & 1u, aph = (it >> 1) & 1u;
+        if (!mbar_wait(bar_acc_empty + 8 * acc, aph ^ 1u, abort_word, kErrTimeoutAccEmpty)) {
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * kBN;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(bar_full + 8 * s, ph, abort_word, kErrTimeoutFull)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t a_addr = smem_base + s * kStageBytes;
+          const uint32_t b_addr = a_addr + kABytes;
+#pragma unroll
+          for (int k = 0; k < kBlockK / kUmmaK; ++k) {
+            const uint64_t adesc = make_smem_desc(a_addr + k * a_step, a_lbo, a_sbo);
+            const uint64_t bdesc = make_smem_desc(b_addr + k * b_step, b_lbo, b_sbo);
+            umma_bf16<kCtaGroup>(d_tmem, adesc, bdesc, idesc, (kb | k) != 0 ? 1u : 0u);
+          }
+          umma_commit<kCtaGroup>(bar_empty + 8 * s);  // frees the stage (in both CTAs) once these MMAs retire
+          if (++s == kStages) {
+            s = 0;
+            ph ^= 1u;
+          }
+        }
+        if (ok) umma_commit<kCtaGroup>(bar_acc_full + 8 * acc);
+      }
+      // Tail: wait until both accumulator stages have been drained, so that no
+      // remote arrive can target this CTA's barriers after it has left.
+      for (int i = 0; i < 2 && ok; ++i, ++it) {
+        const uint32_t acc = it & 1u, aph = (it >> 1) & 1u;
+        ok = mbar_wait(bar_acc_empty + 8 * acc, aph ^ 1u, abort_word, kErrTimeoutAccEmpty);
+      }
+    }
+    __syncwarp();
+  } else {
+    // ============================================================ epilogue
+    const int q = warp & 3;  // TMEM lane quadrant this warp may read
+    const uint32_t acc_empty_sig = (kCtaGroup == 2) ? mapa(bar_acc_empty, 0) : bar_acc_empty;
+    uint32_t it = 0;
+    for (int tile = cluster_id; tile < num_tiles; tile += num_clusters, ++it) {
+      int tm, tn;
+      tile_coords(shape, tile, tm, tn);
+      const uint32_t acc = it & 1u, aph = (it >> 1) & 1u;
+      bool ok = mbar_wait(bar_acc_full + 8 * acc, aph, abort_word, kErrTimeoutAccFull);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tc_fence_after();
+      EpiCtx c;
+      c.row = tm * (kBlockM * kCtaGroup) + static_cast<int>(rank) * kBlockM + q * 32 + lane;
+      c.n0 = tn * kBN;
+      c.tn = tn;
+      c.M = shape.M;
+      c.N = shape.N;
+      c.taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * kBN;
+      c.lane = lane;
+      Epi::template run<kBN>(ep, c, epi_scratch);
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) {
+        if constexpr (kCtaGroup == 2) mbar_arrive_cluster(acc_empty_sig + 8 * acc);
+        else mbar_arrive(bar_acc_empty + 8 * acc);
+      }
+    }
+  }
+
+  // ---------------------------------------------------------------- teardown
+  tc_fence_before();
+  __syncthreads();
+  if constexpr (kCtaGroup == 2) {
+    cluster_arrive();
+    cluster_wait();
+  }
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc<kCtaGroup>(tmem_base, Cfg::kTmemCols);
+  }
+  if (threadIdx.x == 0) {
+    const int code = *abort_word;
+    if (code != 0) atomicMax(status, code);
+  }
+}
+
+}  // namespace cb

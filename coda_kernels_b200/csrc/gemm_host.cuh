@@ -1,0 +1,208 @@
+// Host-side launch glue for the tcgen05 GEMM core: operand description, TMA
+// tensor-map encoding, grid sizing and the (cluster) launch itself.  Nothing in
+// here allocates device memory or synchronises the device.
+#pragma once
+
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <string>
+
+#include "epilogues.cuh"
+
+namespace cb {
+
+// C-ABI return codes.
+enum : int {
+  kOk = 0,
+  kBadArgument = -1,    // shape / alignment / stride the kernels cannot take
+  kBadLayout = -2,      // operand is neither row- nor column-contiguous
+  kCudaError = -3,      // a CUDA runtime call failed
+  kNoDriverEntry = -4,  // cuTensorMapEncodeTiled could not be resolved
+};
+
+inline thread_local std::string g_last_error;
+inline int fail(int code, const std::string& msg) {
+  g_last_error = msg;
+  return code;
+}
+
+// Process-wide tuning / debug options (set through coda_b200_set_option).
+struct Options {
+  int cta_group = 2;  // 1 = one CTA per tile (128 rows), 2 = CTA pair per tile (256 rows)
+  int group_m = 0;    // raster group in tiles; 0 = default
+  int max_ctas = 0;   // cap on the persistent grid; 0 = all SMs
+  int dbg_lbo_mn = 0;
+  int dbg_sbo_mn = 0;
+};
+inline Options& options() {
+  static Options o;
+  return o;
+}
+
+// A 2-D bf16 operand given by its two element strides; exactly one must be 1.
+// `rows` indexes the M (for A) or N (for B) dimension, `depth` the contraction.
+struct Operand {
+  const void* ptr;
+  long long stride_row;    // elements between consecutive rows
+  long long stride_depth;  // elements between consecutive contraction indices
+};
+
+inline bool classify(const Operand& o, long long rows, long long depth, bool* mn_major, long long* ld) {
+  if (o.stride_depth == 1 && (o.stride_row >= depth || rows == 1)) {
+    *mn_major = false;
+    *ld = o.stride_row;
+    return true;
+  }
+  if (o.stride_row == 1 && (o.stride_depth >= rows || depth == 1)) {
+    *mn_major = true;
+    *ld = o.stride_depth;
+    return true;
+  }
+  return false;
+}
+
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                   const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+inline EncodeTiledFn encode_tiled_fn() {
+  static EncodeTiledFn fn = [] {
+    void* f = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &f, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess) {
+      f = nullptr;
+    }
+    return reinterpret_cast<EncodeTiledFn>(f);
+  }();
+  return fn;
+}
+
+// bf16 matrix with `inner` contiguous elements per line and `outer` lines
+// `ld` elements apart; box = 64 x box_outer, 128-byte swizzle, zero fill.
+inline int make_tmap_bf16(CUtensorMap* m, const void* ptr, long long inner, long long outer, long long ld, int box_outer) {
+  EncodeTiledFn fn = encode_tiled_fn();
+  if (!fn) return fail(kNoDriverEntry, "cuTensorMapEncodeTiled not available from the CUDA driver");
+  if ((reinterpret_cast<uintptr_t>(ptr) & 15u) != 0) return fail(kBadArgument, "operand base address must be 16-byte aligned");
+  if (outer > 1 && (ld * 2) % 16 != 0) return fail(kBadArgument, "operand leading dimension must be a multiple of 8 elements");
+  if (inner % 8 != 0) return fail(kBadArgument, "operand contiguous extent must be a multiple of 8 elements");
+  cuuint64_t dims[2] = {static_cast<cuuint64_t>(inner), static_cast<cuuint64_t>(outer)};
+  cuuint64_t strides[1] = {static_cast<cuuint64_t>((outer > 1 ? ld : inner) * 2)};
+  cuuint32_t box[2] = {64u, static_cast<cuuint32_t>(box_outer)};
+  cuuint32_t estr[2] = {1u, 1u};
+  CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(kCudaError, "cuTensorMapEncodeTiled failed with code " + std::to_string(static_cast<int>(r)));
+  return kOk;
+}
+
+inline int sm_count() {
+  static int cached[64] = {0};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+  if (cached[dev] == 0) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+    cached[dev] = n;
+  }
+  return cached[dev];
+}
+
+template <int kCtaGroup, int kBN, bool kAMn, bool kBMn, class Epi>
+int launch_gemm_cfg(const void* a_ptr, long long lda, const void* b_ptr, long long ldb, int M, int N, int K,
+                    const typename Epi::Params& ep, int* status, cudaStream_t stream) {
+  using Cfg = GemmCfg<kCtaGroup, kBN>;
+  CUtensorMap ta, tb;
+  int rc;
+  // K-major: lines run along K; box = 64 k x (rows of the tile).  MN-major: lines run along M/N; box = 64 x 64 k.
+  if (!kAMn) rc = make_tmap_bf16(&ta, a_ptr, K, M, lda, kBlockM);
+  else rc = make_tmap_bf16(&ta, a_ptr, M, K, lda, kBlockK);
+  if (rc != kOk) return rc;
+  if (!kBMn) rc = make_tmap_bf16(&tb, b_ptr, K, N, ldb, Cfg::kBNcta);
+  else rc = make_tmap_bf16(&tb, b_ptr, N, K, ldb, kBlockK);
+  if (rc != kOk) return rc;
+
+  GemmShape shape;
+  shape.M = M;
+  shape.N = N;
+  shape.K = K;
+  const int tile_m = kBlockM * kCtaGroup;
+  shape.tiles_m = (M + tile_m - 1) / tile_m;
+  shape.tiles_n = (N + kBN - 1) / kBN;
+  const Options& opt = options();
+  shape.group_m = opt.group_m > 0 ? opt.group_m : (kCtaGroup == 2 ? 8 : 16);
+  shape.dbg_lbo_mn = opt.dbg_lbo_mn;
+  shape.dbg_sbo_mn = opt.dbg_sbo_mn;
+  const long long num_tiles = static_cast<long long>(shape.tiles_m) * shape.tiles_n;
+  if (num_tiles <= 0 || num_tiles > 0x7fffffffLL) return fail(kBadArgument, "tile count out of range");
+
+  auto kern = gemm_kernel<kCtaGroup, kBN, kAMn, kBMn, Epi>;
+  static bool attr_set[64] = {false};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev >= 0 && dev < 64 && !attr_set[dev]) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(Cfg::kSmemBytes));
+    if (e != cudaSuccess) return fail(kCudaError, std::string("cudaFuncSetAttribute(smem): ") + cudaGetErrorString(e));
+    if (kCtaGroup == 2) {
+      e = cudaFuncSetAttribute(kern, cudaFuncAttributeNonPortableClusterSizeAllowed, 0);
+      (void)e;
+    }
+    attr_set[dev] = true;
+  }
+  int sms = sm_count();
+  if (opt.max_ctas > 0 && opt.max_ctas < sms) sms = opt.max_ctas;
+  int clusters = sms / kCtaGroup;
+  if (clusters < 1) clusters = 1;
+  if (clusters > num_tiles) clusters = static_cast<int>(num_tiles);
+
+  cudaLaunchConfig_t cfg;
+  memset(&cfg, 0, sizeof(cfg));
+  cfg.gridDim = dim3(static_cast<unsigned>(clusters * kCtaGroup), 1, 1);
+  cfg.blockDim = dim3(kNumThreads, 1, 1);
+  cfg.dynamicSmemBytes = Cfg::kSmemBytes;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  if (kCtaGroup == 2) {
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+  }
+  cudaError_t e = cudaLaunchKernelEx(&cfg, kern, ta, tb, shape, ep, status);
+  if (e != cudaSuccess) return fail(kCudaError, std::string("GEMM launch failed: ") + cudaGetErrorString(e));
+  return kOk;
+}
+
+// Dispatch on CTA grouping and operand majors.  kMajors: bit0 = allow A MN-major, bit1 = allow B MN-major.
+template <class Epi, int kAllowMajors>
+int launch_gemm(const Operand& A, const Operand& B, int M, int N, int K, const typename Epi::Params& ep, int* status,
+                cudaStream_t stream) {
+  if (M <= 0 || N <= 0 || K <= 0) return fail(kBadArgument, "GEMM extents must be positive");
+  if (status == nullptr) return fail(kBadArgument, "device status word is required");
+  bool a_mn, b_mn;
+  long long lda, ldb;
+  if (!classify(A, M, K, &a_mn, &lda)) return fail(kBadLayout, "A must be contiguous along one of its two dimensions");
+  if (!classify(B, N, K, &b_mn, &ldb)) return fail(kBadLayout, "B must be contiguous along one of its two dimensions");
+  const bool two = options().cta_group == 2;
+#define CB_LAUNCH(AM, BM)                                                                                          \
+  (two ? launch_gemm_cfg<2, 256, AM, BM, Epi>(A.ptr, lda, B.ptr, ldb, M, N, K, ep, status, stream)                   \
+       : launch_gemm_cfg<1, 256, AM, BM, Epi>(A.ptr, lda, B.ptr, ldb, M, N, K, ep, status, stream))
+  if (!a_mn && !b_mn) return CB_LAUNCH(false, false);
+  if constexpr ((kAllowMajors & 2) != 0) {
+    if (!a_mn && b_mn) return CB_LAUNCH(false, true);
+  }
+  if constexpr ((kAllowMajors & 1) != 0) {
+    if (a_mn && !b_mn) return CB_LAUNCH(true, false);
+  }
+  if constexpr (kAllowMajors == 3) {
+    if (a_mn && b_mn) return CB_LAUNCH(true, true);
+  }
+#undef CB_LAUNCH
+  return fail(kBadLayout, "this fused GEMM needs both operands contiguous along the contraction dimension");
+}
+
+}  // namespace cb

@@ -1,0 +1,67 @@
+// C-ABI entry points for the plain and sigmoid GEMMs, plus library-wide
+// option / error plumbing.  See include/coda_b200.h for the contract.
+#include "../../include/coda_b200.h"
+#include "gemm_host.cuh"
+
+using namespace cb;
+
+extern "C" int coda_b200_version(void) { return 1; }
+
+extern "C" const char* coda_b200_last_error(void) { return g_last_error.c_str(); }
+
+extern "C" int coda_b200_set_option(const char* name, int value) {
+  if (name == nullptr) return fail(kBadArgument, "option name is NULL");
+  Options& o = options();
+  if (!strcmp(name, "cta_group")) {
+    if (value != 1 && value != 2) return fail(kBadArgument, "cta_group must be 1 or 2");
+    o.cta_group = value;
+  } else if (!strcmp(name, "group_m")) {
+    o.group_m = value;
+  } else if (!strcmp(name, "max_ctas")) {
+    o.max_ctas = value;
+  } else if (!strcmp(name, "dbg_lbo_mn")) {
+    o.dbg_lbo_mn = value;
+  } else if (!strcmp(name, "dbg_sbo_mn")) {
+    o.dbg_sbo_mn = value;
+  } else {
+    return fail(kBadArgument, std::string("unknown option: ") + name);
+  }
+  return kOk;
+}
+
+namespace {
+template <typename OutT, Act kAct>
+int run_store(const void* A, int64_t asm_, int64_t ask, const void* B, int64_t bsk, int64_t bsn, void* D, int64_t ldd, int M,
+              int N, int K, const float* alpha, int* dev_status, void* stream) {
+  if (D == nullptr || A == nullptr || B == nullptr) return fail(kBadArgument, "NULL matrix pointer");
+  if ((reinterpret_cast<uintptr_t>(D) & 15u) != 0) return fail(kBadArgument, "D must be 16-byte aligned");
+  if (N % 8 != 0 || ldd % 8 != 0 || ldd < N) return fail(kBadArgument, "N and ldd must be multiples of 8 with ldd >= N");
+  typename EpiStore<OutT, kAct>::Params ep;
+  ep.D = static_cast<OutT*>(D);
+  ep.ldd = ldd;
+  ep.alpha = alpha;
+  Operand a{A, asm_, ask};
+  Operand b{B, bsn, bsk};
+  return launch_gemm<EpiStore<OutT, kAct>, 3>(a, b, M, N, K, ep, dev_status, static_cast<cudaStream_t>(stream));
+}
+}  // namespace
+
+extern "C" int coda_b200_gemm(const void* A, int64_t a_stride_m, int64_t a_stride_k, const void* B, int64_t b_stride_k,
+                              int64_t b_stride_n, void* D, int64_t ldd, int d_is_fp32, int M, int N, int K,
+                              const float* alpha, int* dev_status, void* stream) {
+  if (d_is_fp32)
+    return run_store<float, Act::kNone>(A, a_stride_m, a_stride_k, B, b_stride_k, b_stride_n, D, ldd, M, N, K, alpha,
+                                        dev_status, stream);
+  return run_store<__nv_bfloat16, Act::kNone>(A, a_stride_m, a_stride_k, B, b_stride_k, b_stride_n, D, ldd, M, N, K, alpha,
+                                              dev_status, stream);
+}
+
+extern "C" int coda_b200_gemm_sigmoid(const void* A, int64_t a_stride_m, int64_t a_stride_k, const void* B,
+                                      int64_t b_stride_k, int64_t b_stride_n, void* D, int64_t ldd, int d_is_fp32, int M,
+                                      int N, int K, int* dev_status, void* stream) {
+  if (d_is_fp32)
+    return run_store<float, Act::kSigmoid>(A, a_stride_m, a_stride_k, B, b_stride_k, b_stride_n, D, ldd, M, N, K, nullptr,
+                                           dev_status, stream);
+  return run_store<__nv_bfloat16, Act::kSigmoid>(A, a_stride_m, a_stride_k, B, b_stride_k, b_stride_n, D, ldd, M, N, K,
+                                                 nullptr, dev_status, stream);
+}

@@ -1,0 +1,144 @@
+/*
+ * C ABI of libcoda_b200.so: B200 (sm_100a) kernels behind the fused-linear
+ * operators of coda.kernels.functional.
+ *
+ * Conventions
+ *  - Every pointer is a device pointer unless stated otherwise; the library
+ *    allocates nothing and never synchronises the device.  Work is enqueued on
+ *    `stream` (a cudaStream_t passed as void*; NULL = legacy default stream) of
+ *    the current device.
+ *  - Matrices are bf16 unless stated otherwise.  An operand is described by its
+ *    two element strides, exactly one of which must be 1, so transposed views
+ *    (`w.mT`, `g.mT`) are consumed in place.  Base addresses must be 16-byte
+ *    aligned and leading dimensions multiples of 8 elements.
+ *  - Functions return 0 on success or a negative code (CODA_B200_E*) for
+ *    arguments rejected on the host; coda_b200_last_error() then describes the
+ *    problem.  Device-side trouble (a bounded wait that expired) is reported
+ *    asynchronously through `dev_status`, a device int32 that stays 0 on
+ *    success and receives a positive code otherwise.
+ *
+ * Each entry point names the reference interface it stands in for, as
+ * file:line inside the coda-kernels project.
+ */
+#ifndef CODA_B200_H_
+#define CODA_B200_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define CODA_B200_OK 0
+#define CODA_B200_EARG (-1)    /* bad shape / alignment / stride */
+#define CODA_B200_ELAYOUT (-2) /* operand not contiguous along either dimension */
+#define CODA_B200_ECUDA (-3)   /* CUDA runtime error */
+#define CODA_B200_EDRIVER (-4) /* tensor-map encoder not available */
+
+/* Library version (major * 100 + minor). */
+int coda_b200_version(void);
+
+/* Message for the last non-zero return code on the calling thread. */
+const char* coda_b200_last_error(void);
+
+/* Tuning / debug switches: "cta_group" (1 or 2), "group_m", "max_ctas",
+ * "dbg_lbo_mn", "dbg_sbo_mn".  Returns 0, or CODA_B200_EARG for an unknown name. */
+int coda_b200_set_option(const char* name, int value);
+
+/* D[M,N] = alpha * (A[M,K] @ B[K,N]); D row-major with leading dimension ldd,
+ * bf16 (d_is_fp32 = 0) or fp32 (1); alpha = device fp32 scalar or NULL.
+ * Replaces `coda::_gemm` and `coda::_gemm_scalar_scale_epi`
+ * (coda/core/gemm/functional.py:35-51, 94-113; epilogue coda/core/gemm/epilogues.py:34-36). */
+int coda_b200_gemm(const void* A, int64_t a_stride_m, int64_t a_stride_k, const void* B, int64_t b_stride_k,
+                   int64_t b_stride_n, void* D, int64_t ldd, int d_is_fp32, int M, int N, int K, const float* alpha,
+                   int* dev_status, void* stream);
+
+/* D = sigmoid(A @ B).  Replaces `coda::_gemm_sigmoid_epi`
+ * (coda/core/gemm/functional.py:199-217; epilogue coda/core/gemm/epilogues.py:39-41). */
+int coda_b200_gemm_sigmoid(const void* A, int64_t a_stride_m, int64_t a_stride_k, const void* B, int64_t b_stride_k,
+                           int64_t b_stride_n, void* D, int64_t ldd, int d_is_fp32, int M, int N, int K, int* dev_status,
+                           void* stream);
+
+/* preact[M,N] = bf16(A @ B); postact[M,N/2][:, j] = silu(acc[:, 2j]) * acc[:, 2j+1]
+ * (gate / up columns interleaved).  N must be a multiple of 16.  Replaces
+ * `coda::_gemm_swiglu_epi` (coda/core/gemm/functional.py:237-258; epilogues.py:44-47). */
+int coda_b200_gemm_swiglu(const void* A, int64_t a_stride_m, int64_t a_stride_k, const void* B, int64_t b_stride_k,
+                          int64_t b_stride_n, void* preact, int64_t ld_pre, void* postact, int64_t ld_post, int M, int N,
+                          int K, int* dev_status, void* stream);
+
+/* Number of column tiles the LSE epilogue produces for N columns
+ * (= second extent of part_max / part_sum). */
+int coda_b200_lse_tiles(int N);
+
+/* Log-sum-exp partials of A @ B per (row, column tile): part_max, part_sum
+ * fp32 [M, coda_b200_lse_tiles(N)]; target_logit fp32 [M] receives
+ * acc[i, target[i]] for rows whose int32 target lies in [0, N) (other rows are
+ * left untouched).  If P != NULL, P[M,N] (bf16, leading dimension ldp)
+ * receives exp(acc - tile max): the logits themselves are never stored.
+ * Replaces `coda::_gemm_lse_epi` and `coda::_lse_select_logits_epi`
+ * (coda/core/gemm/functional.py:342-368, 453-493). */
+int coda_b200_gemm_lse(const void* A, int64_t a_stride_m, int64_t a_stride_k, const void* B, int64_t b_stride_k,
+                       int64_t b_stride_n, void* P, int64_t ldp, float* part_max, float* part_sum, const int32_t* target,
+                       float* target_logit, int M, int N, int K, int* dev_status, void* stream);
+
+/* Per row: lse = logsumexp over the tile partials; losses[i] = lse[i] -
+ * target_logit[i], or 0 where target[i] == ignore_index.  lse, losses fp32 [M].
+ * Replaces the `logsumexp(partials)` step and quack `cross_entropy_fwd_out`
+ * call (coda/core/gemm/functional.py:337-339, 484-493). */
+int coda_b200_lse_finalize(const float* part_max, const float* part_sum, int tiles_n, const int32_t* target,
+                           const float* target_logit, int ignore_index, float* lse, float* losses, int M, void* stream);
+
+/* In place: P[i,j] <- exp(tile max - lse[i]) * P[i,j] - (j == target[i]), or +0
+ * for ignored rows; turns the stored probabilities into d(loss_i)/d(logits).
+ * Replaces `cross_entropy_fwd_bwd_kernel`
+ * (coda/core/elementwise/cross_entropy.py:18-131; wrapper coda/core/elementwise/functional.py:221-311). */
+int coda_b200_ce_grad_fixup(void* P, int64_t ldp, const float* part_max, int tiles_n, const float* lse,
+                            const int32_t* target, int ignore_index, int M, int N, void* stream);
+
+/* Fused [q | k | v] projection.  N = (hq + hk + hv) * head_dim columns; q and k
+ * heads get per-head RMSNorm (gamma = [gamma_q | gamma_k], bf16 [2*head_dim])
+ * and interleaved-pair RoPE from `positions` (int32 or fp32 [M]) and
+ * `frequencies` (fp32 [(hq+hk)*head_dim], (hi, lo) turns per pair); v heads are
+ * stored as they are.  Outputs: qk, preact bf16 [M, (hq+hk)*head_dim];
+ * v bf16 [M, hv*head_dim] (may be NULL when N has no v columns);
+ * mean_sq fp32 [M, hq+hk].  head_dim is 64 or 128.  Replaces
+ * `coda::_gemm_qknorm_rope_epi` plus the separate v GEMM
+ * (coda/core/gemm/functional.py:1079-1200; coda/kernels/functional/qknorm_rope.py:27-42). */
+int coda_b200_gemm_qknorm_rope(const void* A, int64_t a_stride_m, int64_t a_stride_k, const void* B, int64_t b_stride_k,
+                               int64_t b_stride_n, void* qk, int64_t ld_qk, void* preact, int64_t ld_pre, void* v,
+                               int64_t ld_v, float* mean_sq, const void* gamma, const void* positions, int pos_is_float,
+                               const float* frequencies, int head_dim, int hq, int hk, float eps, int M, int N, int K,
+                               int* dev_status, void* stream);
+
+/* grad_pre[M,2F] from preact[M,2F] (interleaved gate/up) and dout[M,F]:
+ * dgate = dout*up*(s + g*s*(1-s)), dup = dout*g*s, s = sigmoid(g).
+ * Replaces `dswiglu_backward` (coda/core/elementwise/functional.py:181-218). */
+int coda_b200_dswiglu(const void* preact, int64_t ld_pre, const void* dout, int64_t ld_dout, void* grad_pre, int64_t ld_grad,
+                      int M, int F, void* stream);
+
+/* grad_pre = dout * out * (1 - out), bf16 result; out is bf16 (out_is_fp32 = 0)
+ * or fp32.  Replaces the `aten.sigmoid_backward(...).to(x.dtype)` step of
+ * coda/kernels/functional/sigmoid.py:35. */
+int coda_b200_dsigmoid(const void* out, int64_t ld_out, int out_is_fp32, const void* dout, int64_t ld_dout, void* grad_pre,
+                       int64_t ld_grad, int M, int N, void* stream);
+
+/* Size in bytes of the scratch buffer coda_b200_qknorm_rope_bwd needs. */
+int64_t coda_b200_qknorm_rope_bwd_scratch_bytes(int M, int head_dim);
+
+/* Backward of the q,k epilogue.  dq [M, hq*d], dk [M, hk*d] (row strides ld_dq,
+ * ld_dk); preact, mean_sq as saved by the forward.  Writes grad_pre into
+ * grad[:, :(hq+hk)*d] and, if dv != NULL, copies dv [M, nv] into
+ * grad[:, (hq+hk)*d:], so that one GEMM over `grad` yields dx and one yields
+ * dW.  dgamma fp32 [2*d].  `scratch` holds per-block partial sums of dgamma.
+ * Replaces `qknorm_rope_bwd` (coda/core/elementwise/functional.py:314-456;
+ * kernel coda/core/elementwise/rope.py:19-253). */
+int coda_b200_qknorm_rope_bwd(const void* dq, int64_t ld_dq, const void* dk, int64_t ld_dk, const void* dv, int64_t ld_dv,
+                              int nv, const void* preact, int64_t ld_pre, const float* mean_sq, const void* gamma,
+                              const void* positions, int pos_is_float, const float* frequencies, int head_dim, int hq,
+                              int hk, float eps, void* grad, int64_t ld_grad, float* dgamma, void* scratch,
+                              int64_t scratch_bytes, int M, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* CODA_B200_H_ */
