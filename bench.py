@@ -1,0 +1,461 @@
+"""Benchmark of the fused-linear hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl b200|reference] [--op NAME]
+
+A step is one forward + backward pass of one operator over one batch of seeded
+synthetic input.  The default workload is ``linear_swiglu`` at the Llama-3-8B
+MLP shape (x [16384, 4096], interleaved weight [28672, 4096]); ``--op`` selects
+the other operators of the path at their benchmark shapes.  With ``--gpus N``
+(one process per GPU under ``torch.distributed.run``) the operator is sharded
+column-, head- or vocab-parallel and the total work stays fixed.
+
+Rank 0 prints ONE JSON line.  ``value`` is whole-job TFLOP/s (algorithmic GEMM
+flops only) with inputs resident in HBM; ``e2e`` is the same metric with
+host-to-device copies of the inputs and device-to-host copies of the results
+inside the timed region; ``roofline`` describes the dominant kernel (the fused
+forward GEMM) timed alone; ``cpu_baseline`` is the oracle's eager formulation
+timed on the host cores for a bounded row sample.  ``--impl reference`` times
+that CPU formulation alone, as the reference arm.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+import torch
+
+REPO = Path(__file__).resolve().parent
+if str(REPO) not in sys.path:
+    sys.path.insert(0, str(REPO))
+
+METRIC = "fused GEMM+epilogue TFLOP/s (% of B200 bf16 peak), fwd+bwd, at 1/2/4/8 GPUs"
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
+
+# Benchmark shapes (the operator configurations of the task): see oracle/inputs.py for the distributions.
+SHAPES = {
+    "swiglu": {"M": 16384, "K": 4096, "F": 14336},
+    "sigmoid": {"M": 32768, "K": 5120, "N": 5120},
+    "cross_entropy": {"M": 8192, "K": 4096, "V": 128256},
+    "qknorm_rope": {"M": 16384, "K": 4096, "head_dim": 128, "hq": 32, "hk": 8, "hv": 8, "seq_len": 4096},
+}
+
+
+def algorithmic_flops(op: str, s: dict) -> float:
+    """Forward + backward GEMM flops (3 GEMMs of 2*M*K*N each); recomputation never counts."""
+    if op == "swiglu":
+        n = 2 * s["F"]
+    elif op == "sigmoid":
+        n = s["N"]
+    elif op == "cross_entropy":
+        n = s["V"]
+    else:
+        n = (s["hq"] + s["hk"] + s["hv"]) * s["head_dim"]
+    return 3.0 * 2.0 * s["M"] * s["K"] * n
+
+
+def load_peaks() -> tuple[dict, str]:
+    path = REPO / "MEASURED_PEAKS.json"
+    if path.exists():
+        try:
+            return json.loads(path.read_text()), "measured"
+        except Exception:
+            pass
+    return dict(FALLBACK_PEAKS), "fallback"
+
+
+# ------------------------------------------------------------------------------------------------ clocks
+class ClockSampler:
+    """Samples ``nvidia-smi`` clocks and throttle reasons of one GPU while the timed region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu_index = gpu_index
+        self.rows: list[list[str]] = []
+        self.proc = None
+        self.thread = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", str(self.gpu_index), f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+            return
+        self.thread = threading.Thread(target=self._read, daemon=True)
+        self.thread.start()
+
+    def _read(self):
+        for line in self.proc.stdout:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) == 7:
+                self.rows.append(parts)
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        if self.thread is not None:
+            self.thread.join(timeout=2)
+        sm = []
+        reasons = set()
+        sm_max = None
+        power = []
+        for r in self.rows:
+            try:
+                sm.append(float(r[0]))
+                sm_max = float(r[1])
+                power.append(float(r[2]))
+            except ValueError:
+                continue
+            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), r[3:7]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        # samples under load = upper half of the observed clocks' time span (idle samples bracket the region)
+        return {
+            "sm_mhz": statistics.median(sm) if sm else None,
+            "sm_max_mhz": sm_max,
+            "power_w_max": max(power) if power else None,
+            "samples": len(sm),
+            "reasons": sorted(reasons),
+        }
+
+
+# ------------------------------------------------------------------------------------------------ workloads
+class Workload:
+    """One operator at its benchmark shape, sharded for ``world`` ranks; inputs live on ``device``."""
+
+    def __init__(self, op: str, rank: int, world: int, device: torch.device, pinned_host: bool):
+        import coda_kernels_b200 as ck
+        from coda_kernels_b200 import parallel
+        from oracle import inputs
+
+        self.op, self.rank, self.world, self.device, self.ck, self.parallel = op, rank, world, device, ck, parallel
+        s = SHAPES[op]
+        self.shape = s
+        if op == "swiglu":
+            d = inputs.swiglu_inputs(s["M"], s["K"], s["F"])
+            lo, hi = parallel.shard_bounds(2 * s["F"], rank, world, 16)
+            host = {"x": d["x"], "weight": d["weight"][lo:hi].contiguous(), "dout": d["dout"][:, lo // 2 : hi // 2].contiguous()}
+            self.kernels_per_step = 4  # fused GEMM, dswiglu, dgrad GEMM, wgrad GEMM
+        elif op == "sigmoid":
+            d = inputs.sigmoid_inputs(s["M"], s["K"], s["N"])
+            lo, hi = parallel.shard_bounds(s["N"], rank, world, 8)
+            host = {"x": d["x"], "weight": d["weight"][lo:hi].contiguous(), "dout": d["dout"][:, lo:hi].contiguous()}
+            self.kernels_per_step = 4
+        elif op == "cross_entropy":
+            d = inputs.cross_entropy_inputs(s["M"], s["K"], s["V"])
+            lo, hi = parallel.shard_bounds(s["V"], rank, world, 8)
+            self.vocab_start = lo
+            host = {"x": d["x"], "weight": d["weight"][lo:hi].contiguous(), "target": d["target"]}
+            self.kernels_per_step = 5  # LSE GEMM, finalize, gradient fix-up, dgrad GEMM, wgrad GEMM
+        elif op == "qknorm_rope":
+            d = inputs.qknorm_rope_inputs(s["M"], s["K"], s["head_dim"], s["hq"], s["hk"], s["hv"], s["seq_len"])
+            w, f, hq, hk, hv = parallel.shard_qkv_weight(d["weight"], d["frequencies"], s["head_dim"], s["hq"], s["hk"], s["hv"], rank, world)
+            self.local_heads = (hq, hk, hv)
+            dh = s["head_dim"]
+            host = {
+                "x": d["x"], "weight": w, "gamma": d["gamma"], "positions": d["positions"], "frequencies": f,
+                "dq": d["dq"][:, rank * hq * dh : (rank + 1) * hq * dh].contiguous(),
+                "dk": d["dk"][:, rank * hk * dh : (rank + 1) * hk * dh].contiguous(),
+                "dv": d["dv"][:, rank * hv * dh : (rank + 1) * hv * dh].contiguous(),
+            }
+            self.kernels_per_step = 5  # fused GEMM, qk backward, partial fold, dgrad GEMM, wgrad GEMM
+        else:
+            raise ValueError(op)
+        self.host = {k: (v.pin_memory() if pinned_host else v) for k, v in host.items()}
+        self.dev = {k: v.to(device) for k, v in host.items()}
+        self.h2d_bytes = sum(v.numel() * v.element_size() for v in host.values())
+        self.host_out: dict[str, torch.Tensor] = {}
+
+    def upload(self):
+        for k, v in self.host.items():
+            self.dev[k].copy_(v, non_blocking=True)
+
+    def step(self):
+        """Forward + backward through the public operator API.  Returns the result tensors."""
+        ck, d = self.ck, self.dev
+        x = d["x"].detach().requires_grad_(True)
+        w = d["weight"].detach().requires_grad_(True)
+        if self.op == "swiglu":
+            out = ck.linear_swiglu(x, w)
+            dx, dw = torch.autograd.grad(out, (x, w), d["dout"])
+            return {"out": out, "dx": dx, "dweight": dw}
+        if self.op == "sigmoid":
+            out = ck.linear_sigmoid(x, w)
+            dx, dw = torch.autograd.grad(out, (x, w), d["dout"])
+            return {"out": out, "dx": dx, "dweight": dw}
+        if self.op == "cross_entropy":
+            if self.world == 1:
+                loss = ck.linear_cross_entropy(x, w, d["target"], -100, "mean")
+            else:
+                loss = self.parallel.vocab_parallel_linear_cross_entropy(x, w, d["target"], self.vocab_start, -100, "mean")
+            dx, dw = torch.autograd.grad(loss, (x, w))
+            return {"loss": loss, "dx": dx, "dweight": dw}
+        g = d["gamma"].detach().requires_grad_(True)
+        hq, hk, _ = self.local_heads
+        q, k, v = ck.linear_qknorm_rope(x, w, g, d["positions"], d["frequencies"], self.shape["head_dim"], hq, hk, 1e-6)
+        dx, dw, dg = torch.autograd.grad((q, k, v), (x, w, g), (d["dq"], d["dk"], d["dv"]))
+        if self.world > 1:
+            dg32 = dg.float()
+            torch.distributed.all_reduce(dg32)
+            dg = dg32.to(dg.dtype)
+        return {"q": q, "k": k, "v": v, "dx": dx, "dweight": dw, "dgamma": dg}
+
+    def download(self, results: dict) -> int:
+        nbytes = 0
+        for k, v in results.items():
+            buf = self.host_out.get(k)
+            if buf is None:
+                buf = torch.empty(v.shape, dtype=v.dtype, device="cpu").pin_memory()
+                self.host_out[k] = buf
+            buf.copy_(v, non_blocking=True)
+            nbytes += v.numel() * v.element_size()
+        return nbytes
+
+    def dominant_kernel(self):
+        """(label, callable, flops per launch): the fused forward GEMM of this rank's shard, launched alone."""
+        ck, d, s = self.ck, self.dev, self.shape
+        x, w = d["x"], d["weight"]
+        flops = 2.0 * x.shape[0] * x.shape[1] * w.shape[0]
+        if self.op == "swiglu":
+            return "gemm_kernel<EpiSwiGLU>", (lambda: ck.ops.gemm_swiglu(x, w.mT)), flops
+        if self.op == "sigmoid":
+            return "gemm_kernel<EpiStore<sigmoid>>", (lambda: ck.ops.gemm_sigmoid(x, w.mT)), flops
+        if self.op == "cross_entropy":
+            return "gemm_kernel<EpiLse<store>>", (lambda: ck.ops.gemm_lse_partials(x, w.mT, d["target"], True)), flops
+        hq, hk, _ = self.local_heads
+        return "gemm_kernel<EpiQKNormRope>", (
+            lambda: ck.ops.gemm_qknorm_rope(x, w.mT, d["gamma"], d["positions"], d["frequencies"], s["head_dim"], hq, hk, 1e-6)), flops
+
+
+# ------------------------------------------------------------------------------------------------ CPU formulation (oracle) timing
+def cpu_eager_step(op: str, rows: int, seed_inputs: dict | None = None):
+    """Build a callable that runs the oracle's eager formulation fwd+bwd on ``rows`` rows of the workload on the CPU."""
+    import functools
+
+    from oracle import eager, inputs
+
+    s = dict(SHAPES[op])
+    if op == "swiglu":
+        d = inputs.swiglu_inputs(rows, s["K"], s["F"])
+        fn = lambda: eager.fwd_bwd(eager.linear_swiglu, {"x": d["x"], "weight": d["weight"]}, ["x", "weight"], d["dout"])
+    elif op == "sigmoid":
+        d = inputs.sigmoid_inputs(rows, s["K"], s["N"])
+        fn = lambda: eager.fwd_bwd(eager.linear_sigmoid, {"x": d["x"], "weight": d["weight"]}, ["x", "weight"], d["dout"])
+    elif op == "cross_entropy":
+        d = inputs.cross_entropy_inputs(rows, s["K"], s["V"])
+        ce = functools.partial(eager.linear_cross_entropy, target=d["target"])
+        fn = lambda: eager.fwd_bwd(ce, {"x": d["x"], "weight": d["weight"]}, ["x", "weight"], torch.tensor(1.0))
+    else:
+        d = inputs.qknorm_rope_inputs(rows, s["K"], s["head_dim"], s["hq"], s["hk"], s["hv"], s["seq_len"])
+        qk = functools.partial(eager.linear_qknorm_rope, positions=d["positions"], frequencies=d["frequencies"],
+                               head_dim=s["head_dim"], num_heads_q=s["hq"], num_heads_k=s["hk"], eps=1e-6)
+        fn = lambda: eager.fwd_bwd(qk, {"x": d["x"], "weight": d["weight"], "gamma": d["gamma"]}, ["x", "weight", "gamma"],
+                                   (d["dq"], d["dk"], d["dv"]))
+    s["M"] = rows
+    return fn, algorithmic_flops(op, s)
+
+
+def time_cpu(op: str, rows: int, steps: int, warmup: int) -> tuple[float, float]:
+    """Returns (TFLOP/s, seconds per step) of the CPU eager formulation on a ``rows``-row sample."""
+    fn, flops = cpu_eager_step(op, rows)
+    for _ in range(warmup):
+        fn()
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        fn()
+    dt = (time.perf_counter() - t0) / steps
+    return flops / dt / 1e12, dt
+
+
+def run_reference_arm(args, rank: int) -> None:
+    if rank != 0:
+        return
+    s = SHAPES[args.op]
+    rows = args.cpu_rows or 512
+    tflops, dt = time_cpu(args.op, rows, args.steps, max(args.warmup, 1))
+    cores = torch.get_num_threads()
+    sample = f"rows 0..{rows - 1} of {s['M']} (full K and output width), fwd+bwd, oracle eager formulation in fp32 on bf16 inputs"
+    line = {
+        "impl": "reference", "metric": METRIC, "value": tflops, "unit": "TFLOP/s", "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": workload_name(args.op), **s, "parallelism": f"cpu x{cores} threads", "l2": "n/a (host)"},
+        "cpu_baseline": {"value": tflops, "unit": "TFLOP/s", "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": tflops, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def workload_name(op: str) -> str:
+    return {
+        "swiglu": "linear_swiglu fwd+bwd, Llama-3-8B MLP: x[16384,4096] W[28672,4096] interleaved gate/up",
+        "sigmoid": "linear_sigmoid fwd+bwd: x[32768,5120] W[5120,5120]",
+        "cross_entropy": "linear_cross_entropy fwd+bwd: x[8192,4096] W[128256,4096], 5% ignored, mean",
+        "qknorm_rope": "linear_qknorm_rope fwd+bwd: x[16384,4096] W[6144,4096], GQA 32/8/8 x128, theta 5e5",
+    }[op]
+
+
+# ------------------------------------------------------------------------------------------------ main
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--op", default="swiglu", choices=list(SHAPES))
+    ap.add_argument("--cpu-rows", type=int, default=0, help="rows of the CPU-baseline sample (0 = default)")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--reduce-dx", action="store_true", help="all-reduce the partial dx over ranks inside the step")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
+
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+
+    if args.impl == "reference":
+        run_reference_arm(args, rank)
+        return
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the operators have no CPU fallback")
+    device = torch.device("cuda", local_rank)
+    torch.cuda.set_device(device)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        torch.distributed.init_process_group("nccl", device_id=device)
+
+    def barrier():
+        if world > 1:
+            torch.distributed.barrier()
+        torch.cuda.synchronize()
+
+    wl = Workload(args.op, rank, world, device, pinned_host=not args.no_e2e)
+    from coda_kernels_b200 import ops, parallel
+
+    def full_step():
+        res = wl.step()
+        if args.reduce_dx and world > 1:
+            parallel.allreduce_partial_dx(res["dx"])
+        return res
+
+    # ---- device-resident timing
+    for _ in range(args.warmup):
+        full_step()
+    barrier()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+        time.sleep(0.3)
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        res = full_step()
+    e1.record()
+    barrier()
+    ms_total = e0.elapsed_time(e1)
+    clocks = sampler.stop() if rank == 0 else None
+    ops.check_device_status(device)
+    t = torch.tensor([ms_total], device=device)
+    if world > 1:
+        torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
+    ms_step = float(t.item()) / args.steps
+    flops = algorithmic_flops(args.op, SHAPES[args.op])
+    value = flops / (ms_step * 1e-3) / 1e12
+
+    # ---- end to end: host buffers in, host buffers out, every step
+    e2e = None
+    if not args.no_e2e:
+        d2h = 0
+        for _ in range(2):
+            wl.upload()
+            d2h = wl.download(full_step())
+        barrier()
+        e0.record()
+        for _ in range(args.steps):
+            wl.upload()
+            d2h = wl.download(full_step())
+        e1.record()
+        barrier()
+        t = torch.tensor([e0.elapsed_time(e1)], device=device)
+        if world > 1:
+            torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
+        e2e_ms = float(t.item()) / args.steps
+        e2e = {"value": flops / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": e2e_ms,
+               "h2d_bytes_per_step": wl.h2d_bytes, "d2h_bytes_per_step": d2h}
+
+    # ---- dominant kernel alone, for the roofline
+    peaks, peak_kind = load_peaks()
+    label, launch, k_flops = wl.dominant_kernel()
+    for _ in range(3):
+        launch()
+    torch.cuda.synchronize()
+    n_k = max(args.steps, 10)
+    e0.record()
+    for _ in range(n_k):
+        launch()
+    e1.record()
+    torch.cuda.synchronize()
+    k_ms = e0.elapsed_time(e1) / n_k
+    achieved = k_flops / (k_ms * 1e-3) / 1e12
+    peak = float(peaks.get("bf16_tflops", FALLBACK_PEAKS["bf16_tflops"]))
+    traffic_path = REPO / "profiles" / f"traffic_{args.op}.json"
+    traffic = None
+    if traffic_path.exists():
+        try:
+            traffic = json.loads(traffic_path.read_text()).get("dram_bytes_per_launch")
+        except Exception:
+            traffic = None
+    roofline = {"bound": "tensor", "kernel": label, "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
+                "peak_kind": f"{peak_kind} burst bf16 (kernel timed alone)", "ms_per_launch": k_ms, "flops_per_launch": k_flops,
+                "traffic": traffic}
+
+    # ---- CPU baseline (rank 0, single GPU run only)
+    cpu = None
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        rows = args.cpu_rows or 1024
+        tf, dt = time_cpu(args.op, rows, steps=2, warmup=1)
+        cpu = {"value": tf, "unit": "TFLOP/s", "cores": torch.get_num_threads(), "kind": "port", "seconds_per_sample_step": dt,
+               "sample": f"rows 0..{rows - 1} of {SHAPES[args.op]['M']} (full K and output width), fwd+bwd, 1 warm-up + 2 timed"}
+
+    if rank == 0:
+        s = SHAPES[args.op]
+        line = {
+            "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
+            "data": "synthetic",
+            "config": {"workload": workload_name(args.op), **s, "global_batch_tokens": s["M"],
+                       "parallelism": {"swiglu": "column", "sigmoid": "column", "cross_entropy": "vocab", "qknorm_rope": "head"}[args.op] + f"-parallel x{world}",
+                       "dx_allreduce": bool(args.reduce_dx and world > 1),
+                       "l2": f"no flush: each step streams {wl.h2d_bytes / 1e6:.0f} MB of inputs plus larger intermediates, above the 126 MB L2"},
+            "tokens_per_s": s["M"] / (ms_step * 1e-3),
+            "frac_of_peak": value / (world * peak),
+            "frac_of_sustained_peak": value / (world * float(peaks.get("bf16_tflops_sustained", FALLBACK_PEAKS["bf16_tflops_sustained"]))),
+            "clocks": clocks, "e2e": e2e, "gpu_launches": wl.kernels_per_step * args.steps, "roofline": roofline, "cpu_baseline": cpu,
+        }
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        torch.distributed.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,84 @@
+"""ctypes binding of ``libcoda_b200.so`` (the C ABI declared in ``include/coda_b200.h``).
+
+The library is built in-tree by :mod:`coda_kernels_b200.build`.  There is no
+fallback: if the shared object is missing or a symbol cannot be resolved, the
+import of this module raises, and every operator built on it fails loudly.
+"""
+
+from __future__ import annotations
+
+import ctypes
+import os
+from ctypes import c_char_p, c_float, c_int, c_int64, c_void_p
+from pathlib import Path
+
+_PKG_DIR = Path(__file__).resolve().parent
+LIB_PATH = _PKG_DIR / "libcoda_b200.so"
+
+_P = c_void_p
+_I = c_int
+_L = c_int64
+_F = c_float
+
+# name -> (restype, argtypes); mirrors include/coda_b200.h one to one.
+SIGNATURES = {
+    "coda_b200_version": (_I, []),
+    "coda_b200_last_error": (c_char_p, []),
+    "coda_b200_set_option": (_I, [c_char_p, _I]),
+    "coda_b200_gemm": (_I, [_P, _L, _L, _P, _L, _L, _P, _L, _I, _I, _I, _I, _P, _P, _P]),
+    "coda_b200_gemm_sigmoid": (_I, [_P, _L, _L, _P, _L, _L, _P, _L, _I, _I, _I, _I, _P, _P]),
+    "coda_b200_gemm_swiglu": (_I, [_P, _L, _L, _P, _L, _L, _P, _L, _P, _L, _I, _I, _I, _P, _P]),
+    "coda_b200_lse_tiles": (_I, [_I]),
+    "coda_b200_gemm_lse": (_I, [_P, _L, _L, _P, _L, _L, _P, _L, _P, _P, _P, _P, _I, _I, _I, _P, _P]),
+    "coda_b200_lse_finalize": (_I, [_P, _P, _I, _P, _P, _I, _P, _P, _I, _P]),
+    "coda_b200_ce_grad_fixup": (_I, [_P, _L, _P, _I, _P, _P, _I, _I, _I, _P]),
+    "coda_b200_gemm_qknorm_rope": (
+        _I,
+        [_P, _L, _L, _P, _L, _L, _P, _L, _P, _L, _P, _L, _P, _P, _P, _I, _P, _I, _I, _I, _F, _I, _I, _I, _P, _P],
+    ),
+    "coda_b200_dswiglu": (_I, [_P, _L, _P, _L, _P, _L, _I, _I, _P]),
+    "coda_b200_dsigmoid": (_I, [_P, _L, _I, _P, _L, _P, _L, _I, _I, _P]),
+    "coda_b200_qknorm_rope_bwd_scratch_bytes": (_L, [_I, _I]),
+    "coda_b200_qknorm_rope_bwd": (
+        _I,
+        [_P, _L, _P, _L, _P, _L, _I, _P, _L, _P, _P, _P, _I, _P, _I, _I, _I, _F, _P, _L, _P, _P, _L, _I, _P],
+    ),
+}
+
+
+def _load() -> ctypes.CDLL:
+    if os.environ.get("CODA_B200_BUILD_ON_IMPORT", "1") == "1":
+        from . import build as _build
+
+        # Rebuild when the sources changed since the library was built (needs nvcc; skipped silently without it,
+        # in which case a missing library is the error reported below).
+        if _build.is_stale() and _build.have_nvcc():
+            _build.build_library()
+    if not LIB_PATH.exists():
+        raise ImportError(
+            f"{LIB_PATH} is missing: build it with `python -m coda_kernels_b200.build` "
+            "(needs nvcc; there is no CPU or eager fallback)"
+        )
+    lib = ctypes.CDLL(str(LIB_PATH))
+    for name, (restype, argtypes) in SIGNATURES.items():
+        fn = getattr(lib, name)  # raises AttributeError if the symbol is absent
+        fn.restype = restype
+        fn.argtypes = argtypes
+    return lib
+
+
+lib = _load()
+
+
+class CodaB200Error(RuntimeError):
+    """A C-ABI call rejected its arguments or a CUDA call failed."""
+
+
+def check(rc: int, what: str) -> None:
+    if rc != 0:
+        msg = lib.coda_b200_last_error()
+        raise CodaB200Error(f"{what} failed (code {rc}): {msg.decode() if msg else ''}")
+
+
+def set_option(name: str, value: int) -> None:
+    check(lib.coda_b200_set_option(name.encode(), int(value)), f"set_option({name})")

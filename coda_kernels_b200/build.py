@@ -8,6 +8,7 @@ next to this file, so that the binary travels with the source tree.
 
 from __future__ import annotations
 
+import hashlib
 import os
 import shutil
 import subprocess
@@ -18,6 +19,7 @@ from pathlib import Path
 PKG_DIR = Path(__file__).resolve().parent
 CSRC = PKG_DIR / "csrc"
 LIB_PATH = PKG_DIR / "libcoda_b200.so"
+HASH_PATH = PKG_DIR / "libcoda_b200.srchash"
 OBJ_DIR = PKG_DIR / "build"
 
 NVCC_FLAGS = [
@@ -39,17 +41,29 @@ def _nvcc() -> str:
     return nvcc
 
 
+def have_nvcc() -> bool:
+    return bool(shutil.which("nvcc")) or os.path.exists("/usr/local/cuda/bin/nvcc")
+
+
 def _sources() -> list[Path]:
     return sorted(CSRC.glob("*.cu"))
 
 
-def _deps_mtime() -> float:
-    files = list(CSRC.glob("*.cu")) + list(CSRC.glob("*.cuh")) + [PKG_DIR.parent / "include" / "coda_b200.h"]
-    return max(f.stat().st_mtime for f in files if f.exists())
+def source_hash() -> str:
+    """Digest of every file the library is built from (content, not mtime: copies of the tree keep it)."""
+    h = hashlib.sha256()
+    files = sorted(CSRC.glob("*.cu")) + sorted(CSRC.glob("*.cuh")) + [PKG_DIR.parent / "include" / "coda_b200.h"]
+    for f in files:
+        h.update(f.name.encode())
+        h.update(f.read_bytes())
+    h.update(" ".join(NVCC_FLAGS).encode())
+    return h.hexdigest()
 
 
 def is_stale() -> bool:
-    return (not LIB_PATH.exists()) or LIB_PATH.stat().st_mtime < _deps_mtime()
+    if not LIB_PATH.exists() or not HASH_PATH.exists():
+        return True
+    return HASH_PATH.read_text().strip() != source_hash()
 
 
 def build_library(force: bool = False, verbose: bool = False) -> Path:
@@ -80,6 +94,7 @@ def build_library(force: bool = False, verbose: bool = False) -> Path:
     res = subprocess.run(link, capture_output=True, text=True)
     if res.returncode != 0:
         raise RuntimeError(f"link failed:\n{res.stdout}\n{res.stderr}")
+    HASH_PATH.write_text(source_hash() + "\n")
     return LIB_PATH
 
 

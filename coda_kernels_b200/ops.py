@@ -1,0 +1,390 @@
+"""Device operators: ``torch.library`` custom ops over the C ABI of ``libcoda_b200.so``.
+
+This is the layer that stands in for ``coda/core/gemm/functional.py`` and
+``coda/core/elementwise/functional.py`` of the reference: every device op is a
+mutating custom op that returns ``None`` (outputs are allocated by the Python
+wrapper and passed in), with a no-op fake implementation so that the ops trace
+under ``torch.compile(fullgraph=True)`` — the convention of
+``coda/core/gemm/gemm_interface.py:78-100``.  PyTorch only provides device
+memory and the current stream; all arithmetic runs in the library's kernels.
+"""
+
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+from torch import Tensor
+
+from ._lib import check, lib
+
+_BF16 = torch.bfloat16
+_status_words: dict[int, Tensor] = {}
+
+
+def status_word(device: torch.device) -> Tensor:
+    """Per-device int32 word that kernels set when a bounded wait expires."""
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    word = _status_words.get(idx)
+    if word is None:
+        word = torch.zeros(1, dtype=torch.int32, device=torch.device("cuda", idx))
+        _status_words[idx] = word
+    return word
+
+
+def check_device_status(device: Optional[torch.device] = None) -> None:
+    """Synchronously read the status word; raise if any kernel reported trouble."""
+    device = device if device is not None else torch.device("cuda", torch.cuda.current_device())
+    code = int(status_word(device).item())
+    if code != 0:
+        status_word(device).zero_()
+        raise RuntimeError(f"coda_b200 kernel reported device-side error code {code} (a bounded wait expired)")
+
+
+def _stream(t: Tensor) -> int:
+    return torch.cuda.current_stream(t.device).cuda_stream
+
+
+def _require(cond: bool, msg: str) -> None:
+    if not cond:
+        raise ValueError(msg)
+
+
+def _require_cuda_bf16(*tensors: Tensor) -> None:
+    for t in tensors:
+        if not t.is_cuda:
+            raise RuntimeError("coda_b200 operators run on CUDA tensors only; there is no CPU fallback")
+        if t.dtype != _BF16:
+            raise NotImplementedError(f"coda_b200 operators take bfloat16 matrices, got {t.dtype}")
+
+
+def _noop_fake(*args, **kwargs) -> None:
+    return None
+
+
+# ------------------------------------------------------------------------------------------------ custom ops
+
+
+@torch.library.custom_op("coda_b200::gemm_out", mutates_args=("out",), device_types="cuda")
+def _gemm_out(A: Tensor, B: Tensor, out: Tensor, alpha: Optional[Tensor]) -> None:
+    M, K = A.shape
+    N = B.shape[1]
+    check(
+        lib.coda_b200_gemm(
+            A.data_ptr(), A.stride(0), A.stride(1), B.data_ptr(), B.stride(0), B.stride(1), out.data_ptr(), out.stride(0),
+            int(out.dtype == torch.float32), M, N, K, alpha.data_ptr() if alpha is not None else None,
+            status_word(A.device).data_ptr(), _stream(A),
+        ),
+        "gemm",
+    )
+
+
+@torch.library.custom_op("coda_b200::gemm_sigmoid_out", mutates_args=("out",), device_types="cuda")
+def _gemm_sigmoid_out(A: Tensor, B: Tensor, out: Tensor) -> None:
+    M, K = A.shape
+    N = B.shape[1]
+    check(
+        lib.coda_b200_gemm_sigmoid(
+            A.data_ptr(), A.stride(0), A.stride(1), B.data_ptr(), B.stride(0), B.stride(1), out.data_ptr(), out.stride(0),
+            int(out.dtype == torch.float32), M, N, K, status_word(A.device).data_ptr(), _stream(A),
+        ),
+        "gemm_sigmoid",
+    )
+
+
+@torch.library.custom_op("coda_b200::gemm_swiglu_out", mutates_args=("preact", "postact"), device_types="cuda")
+def _gemm_swiglu_out(A: Tensor, B: Tensor, preact: Tensor, postact: Tensor) -> None:
+    M, K = A.shape
+    N = B.shape[1]
+    check(
+        lib.coda_b200_gemm_swiglu(
+            A.data_ptr(), A.stride(0), A.stride(1), B.data_ptr(), B.stride(0), B.stride(1), preact.data_ptr(),
+            preact.stride(0), postact.data_ptr(), postact.stride(0), M, N, K, status_word(A.device).data_ptr(), _stream(A),
+        ),
+        "gemm_swiglu",
+    )
+
+
+@torch.library.custom_op(
+    "coda_b200::gemm_lse_out", mutates_args=("probs", "part_max", "part_sum", "target_logit"), device_types="cuda"
+)
+def _gemm_lse_out(
+    A: Tensor, B: Tensor, probs: Optional[Tensor], part_max: Tensor, part_sum: Tensor, target: Tensor, target_logit: Tensor
+) -> None:
+    M, K = A.shape
+    N = B.shape[1]
+    check(
+        lib.coda_b200_gemm_lse(
+            A.data_ptr(), A.stride(0), A.stride(1), B.data_ptr(), B.stride(0), B.stride(1),
+            probs.data_ptr() if probs is not None else None, probs.stride(0) if probs is not None else 0,
+            part_max.data_ptr(), part_sum.data_ptr(), target.data_ptr(), target_logit.data_ptr(), M, N, K,
+            status_word(A.device).data_ptr(), _stream(A),
+        ),
+        "gemm_lse",
+    )
+
+
+@torch.library.custom_op("coda_b200::lse_finalize_out", mutates_args=("lse", "losses"), device_types="cuda")
+def _lse_finalize_out(
+    part_max: Tensor, part_sum: Tensor, target: Tensor, target_logit: Tensor, ignore_index: int, lse: Tensor, losses: Tensor
+) -> None:
+    M, tiles = part_max.shape
+    check(
+        lib.coda_b200_lse_finalize(
+            part_max.data_ptr(), part_sum.data_ptr(), tiles, target.data_ptr(), target_logit.data_ptr(), ignore_index,
+            lse.data_ptr(), losses.data_ptr(), M, _stream(part_max),
+        ),
+        "lse_finalize",
+    )
+
+
+@torch.library.custom_op("coda_b200::ce_grad_fixup_", mutates_args=("probs",), device_types="cuda")
+def _ce_grad_fixup(probs: Tensor, part_max: Tensor, lse: Tensor, target: Tensor, ignore_index: int) -> None:
+    M, N = probs.shape
+    check(
+        lib.coda_b200_ce_grad_fixup(
+            probs.data_ptr(), probs.stride(0), part_max.data_ptr(), part_max.shape[1], lse.data_ptr(), target.data_ptr(),
+            ignore_index, M, N, _stream(probs),
+        ),
+        "ce_grad_fixup",
+    )
+
+
+@torch.library.custom_op(
+    "coda_b200::gemm_qknorm_rope_out", mutates_args=("qk", "preact", "v", "mean_sq"), device_types="cuda"
+)
+def _gemm_qknorm_rope_out(
+    A: Tensor, B: Tensor, qk: Tensor, preact: Tensor, v: Optional[Tensor], mean_sq: Tensor, gamma: Tensor, positions: Tensor,
+    frequencies: Tensor, head_dim: int, num_heads_q: int, num_heads_k: int, eps: float,
+) -> None:
+    M, K = A.shape
+    N = B.shape[1]
+    check(
+        lib.coda_b200_gemm_qknorm_rope(
+            A.data_ptr(), A.stride(0), A.stride(1), B.data_ptr(), B.stride(0), B.stride(1), qk.data_ptr(), qk.stride(0),
+            preact.data_ptr(), preact.stride(0), v.data_ptr() if v is not None else None, v.stride(0) if v is not None else 0,
+            mean_sq.data_ptr(), gamma.data_ptr(), positions.data_ptr(), int(positions.dtype == torch.float32),
+            frequencies.data_ptr(), head_dim, num_heads_q, num_heads_k, float(eps), M, N, K,
+            status_word(A.device).data_ptr(), _stream(A),
+        ),
+        "gemm_qknorm_rope",
+    )
+
+
+@torch.library.custom_op("coda_b200::dswiglu_out", mutates_args=("grad_pre",), device_types="cuda")
+def _dswiglu_out(preact: Tensor, dout: Tensor, grad_pre: Tensor) -> None:
+    M, F = dout.shape
+    check(
+        lib.coda_b200_dswiglu(
+            preact.data_ptr(), preact.stride(0), dout.data_ptr(), dout.stride(0), grad_pre.data_ptr(), grad_pre.stride(0), M, F,
+            _stream(dout),
+        ),
+        "dswiglu",
+    )
+
+
+@torch.library.custom_op("coda_b200::dsigmoid_out", mutates_args=("grad_pre",), device_types="cuda")
+def _dsigmoid_out(out: Tensor, dout: Tensor, grad_pre: Tensor) -> None:
+    M, N = dout.shape
+    check(
+        lib.coda_b200_dsigmoid(
+            out.data_ptr(), out.stride(0), int(out.dtype == torch.float32), dout.data_ptr(), dout.stride(0),
+            grad_pre.data_ptr(), grad_pre.stride(0), M, N, _stream(dout),
+        ),
+        "dsigmoid",
+    )
+
+
+@torch.library.custom_op("coda_b200::qknorm_rope_bwd_out", mutates_args=("grad", "dgamma", "scratch"), device_types="cuda")
+def _qknorm_rope_bwd_out(
+    dq: Tensor, dk: Tensor, dv: Optional[Tensor], preact: Tensor, mean_sq: Tensor, gamma: Tensor, positions: Tensor,
+    frequencies: Tensor, head_dim: int, num_heads_q: int, num_heads_k: int, eps: float, grad: Tensor, dgamma: Tensor,
+    scratch: Tensor,
+) -> None:
+    M = preact.shape[0]
+    check(
+        lib.coda_b200_qknorm_rope_bwd(
+            dq.data_ptr(), dq.stride(0), dk.data_ptr(), dk.stride(0), dv.data_ptr() if dv is not None else None,
+            dv.stride(0) if dv is not None else 0, dv.shape[1] if dv is not None else 0, preact.data_ptr(), preact.stride(0),
+            mean_sq.data_ptr(), gamma.data_ptr(), positions.data_ptr(), int(positions.dtype == torch.float32),
+            frequencies.data_ptr(), head_dim, num_heads_q, num_heads_k, float(eps), grad.data_ptr(), grad.stride(0),
+            dgamma.data_ptr(), scratch.data_ptr(), scratch.numel() * scratch.element_size(), M, _stream(preact),
+        ),
+        "qknorm_rope_bwd",
+    )
+
+
+for _op in (
+    _gemm_out, _gemm_sigmoid_out, _gemm_swiglu_out, _gemm_lse_out, _lse_finalize_out, _ce_grad_fixup, _gemm_qknorm_rope_out,
+    _dswiglu_out, _dsigmoid_out, _qknorm_rope_bwd_out,
+):
+    _op.register_fake(_noop_fake)
+
+
+# ------------------------------------------------------------------------------------------------ python wrappers
+
+
+def gemm(A: Tensor, B: Tensor, out: Optional[Tensor] = None, alpha: Optional[Tensor] = None,
+         out_dtype: Optional[torch.dtype] = None) -> Tensor:
+    """``out = alpha * (A @ B)`` for ``A[M,K]``, ``B[K,N]`` (any mix of plain and ``.mT`` views).
+
+    Counterpart of ``gemm`` / ``gemm_scalar_scale`` (coda/core/gemm/functional.py:54-69, 116-132).
+    ``alpha`` is a 0-d or 1-element fp32 device tensor (no host sync).
+    """
+    _require_cuda_bf16(A, B)
+    _require(A.dim() == 2 and B.dim() == 2 and A.shape[1] == B.shape[0], "gemm: A[M,K] @ B[K,N] expected")
+    if out is None:
+        out = torch.empty(A.shape[0], B.shape[1], dtype=out_dtype or A.dtype, device=A.device)
+    _require(out.dtype in (_BF16, torch.float32), "gemm: out must be bfloat16 or float32")
+    _require(out.dim() == 2 and out.stride(1) == 1 and tuple(out.shape) == (A.shape[0], B.shape[1]), "gemm: bad out")
+    if alpha is not None:
+        _require(alpha.dtype == torch.float32 and alpha.numel() == 1 and alpha.is_cuda, "gemm: alpha must be a 1-element fp32 CUDA tensor")
+    _gemm_out(A, B, out, alpha)
+    return out
+
+
+def gemm_scalar_scale(A: Tensor, B: Tensor, alpha: Tensor, out: Optional[Tensor] = None) -> Tensor:
+    return gemm(A, B, out=out, alpha=alpha)
+
+
+def gemm_sigmoid(A: Tensor, B: Tensor, out: Optional[Tensor] = None) -> Tensor:
+    """``sigmoid(A @ B)``; counterpart of coda/core/gemm/functional.py:220-234."""
+    _require_cuda_bf16(A, B)
+    if out is None:
+        out = torch.empty(A.shape[0], B.shape[1], dtype=A.dtype, device=A.device)
+    _require(out.dtype in (_BF16, torch.float32), "gemm_sigmoid: out must be bfloat16 or float32")
+    _require(out.stride(1) == 1 and tuple(out.shape) == (A.shape[0], B.shape[1]), "gemm_sigmoid: bad out")
+    _gemm_sigmoid_out(A, B, out)
+    return out
+
+
+def gemm_swiglu(A: Tensor, B: Tensor) -> tuple[Tensor, Tensor]:
+    """``(preact, postact)`` with interleaved gate/up columns; counterpart of coda/core/gemm/functional.py:261-280."""
+    _require_cuda_bf16(A, B)
+    M, N = A.shape[0], B.shape[1]
+    _require(N % 2 == 0, "gemm_swiglu: N must be even")
+    preact = torch.empty(M, N, dtype=A.dtype, device=A.device)
+    postact = torch.empty(M, N // 2, dtype=A.dtype, device=A.device)
+    _gemm_swiglu_out(A, B, preact, postact)
+    return preact, postact
+
+
+def lse_tiles(N: int) -> int:
+    return int(lib.coda_b200_lse_tiles(int(N)))
+
+
+def gemm_lse_partials(A: Tensor, B: Tensor, target: Tensor, store_probs: bool) -> tuple[Optional[Tensor], Tensor, Tensor, Tensor]:
+    """Run the LSE GEMM.  Returns ``(probs or None, part_max, part_sum, target_logit)``."""
+    _require_cuda_bf16(A, B)
+    _require(target.dtype == torch.int32 and target.is_cuda and target.is_contiguous(), "target must be a contiguous int32 CUDA tensor")
+    M, N = A.shape[0], B.shape[1]
+    tiles = lse_tiles(N)
+    probs = torch.empty(M, N, dtype=A.dtype, device=A.device) if store_probs else None
+    part_max = torch.empty(M, tiles, dtype=torch.float32, device=A.device)
+    part_sum = torch.empty(M, tiles, dtype=torch.float32, device=A.device)
+    target_logit = torch.zeros(M, dtype=torch.float32, device=A.device)
+    _gemm_lse_out(A, B, probs, part_max, part_sum, target, target_logit)
+    return probs, part_max, part_sum, target_logit
+
+
+def lse_finalize(part_max: Tensor, part_sum: Tensor, target: Tensor, target_logit: Tensor, ignore_index: int) -> tuple[Tensor, Tensor]:
+    M = part_max.shape[0]
+    lse = torch.empty(M, dtype=torch.float32, device=part_max.device)
+    losses = torch.empty(M, dtype=torch.float32, device=part_max.device)
+    _lse_finalize_out(part_max, part_sum, target, target_logit, int(ignore_index), lse, losses)
+    return lse, losses
+
+
+def gemm_lse_select_logits(A: Tensor, B: Tensor, target: Tensor, ignore_index: int) -> tuple[Tensor, Tensor, Tensor]:
+    """Per-row ``(loss, lse, target_logit)`` without storing anything of size [M, N].
+
+    Counterpart of ``gemm_lse_select_logits`` (coda/core/gemm/functional.py:496-527).
+    """
+    _, part_max, part_sum, target_logit = gemm_lse_partials(A, B, target, store_probs=False)
+    lse, losses = lse_finalize(part_max, part_sum, target, target_logit, ignore_index)
+    return losses, lse, target_logit
+
+
+def gemm_lse_dlogits(A: Tensor, B: Tensor, target: Tensor, ignore_index: int) -> tuple[Tensor, Tensor]:
+    """Per-row losses and the bf16 gradient of each row's loss w.r.t. the logits.
+
+    Counterpart of ``gemm_lse`` + ``cross_entropy_fwd_bwd``
+    (coda/kernels/functional/cross_entropy.py:25-47); the [M, N] buffer holds
+    unnormalised probabilities first and the gradient after the in-place pass,
+    never the logits.
+    """
+    probs, part_max, part_sum, target_logit = gemm_lse_partials(A, B, target, store_probs=True)
+    lse, losses = lse_finalize(part_max, part_sum, target, target_logit, ignore_index)
+    _ce_grad_fixup(probs, part_max, lse, target, int(ignore_index))
+    return losses, probs
+
+
+def gemm_qknorm_rope(
+    A: Tensor, B: Tensor, weight: Tensor, positions: Tensor, frequencies: Tensor, head_dim: int, num_heads_q: int,
+    num_heads_k: int, eps: float,
+) -> tuple[Tensor, Tensor, Tensor, Optional[Tensor]]:
+    """Fused ``[q | k | v]`` projection: returns ``(qk, preact, head_mean_sq, v)``.
+
+    ``B`` is ``W.mT`` of the whole ``[(hq+hk+hv)*d, K]`` weight (``v`` is ``None``
+    when it has no v rows).  Counterpart of ``gemm_qknorm_rope``
+    (coda/core/gemm/functional.py:1155-1200) plus the v GEMM of
+    coda/kernels/functional/qknorm_rope.py:39.
+    """
+    _require_cuda_bf16(A, B, weight)
+    _require(positions.dtype in (torch.int32, torch.float32), "positions must be int32 or float32")
+    _require(frequencies.dtype == torch.float32, "frequencies must be float32")
+    M, N = A.shape[0], B.shape[1]
+    heads = num_heads_q + num_heads_k
+    size_qk = heads * head_dim
+    _require(weight.numel() == 2 * head_dim, "gamma must hold [gamma_q | gamma_k]")
+    _require(frequencies.numel() == size_qk, "frequencies must have (hq + hk) * head_dim entries")
+    _require(positions.numel() == M, "positions must have one entry per row")
+    qk = torch.empty(M, size_qk, dtype=A.dtype, device=A.device)
+    preact = torch.empty(M, size_qk, dtype=A.dtype, device=A.device)
+    mean_sq = torch.empty(M, heads, dtype=torch.float32, device=A.device)
+    v = torch.empty(M, N - size_qk, dtype=A.dtype, device=A.device) if N > size_qk else None
+    _gemm_qknorm_rope_out(
+        A, B, qk, preact, v, mean_sq, weight.contiguous(), positions.contiguous(), frequencies.contiguous(), head_dim,
+        num_heads_q, num_heads_k, float(eps),
+    )
+    return qk, preact, mean_sq, v
+
+
+def dswiglu_backward(preact: Tensor, dout: Tensor) -> Tensor:
+    """Counterpart of ``dswiglu_backward`` (coda/core/elementwise/functional.py:202-218)."""
+    _require_cuda_bf16(preact, dout)
+    _require(preact.stride(1) == 1 and dout.stride(1) == 1 and preact.shape[1] == 2 * dout.shape[1], "dswiglu: bad shapes")
+    grad_pre = torch.empty_like(preact)
+    _dswiglu_out(preact, dout, grad_pre)
+    return grad_pre
+
+
+def dsigmoid_backward(out: Tensor, dout: Tensor) -> Tensor:
+    """``dout * out * (1 - out)`` in bf16 (the ``sigmoid_backward(...).to(x.dtype)`` step of sigmoid.py:35)."""
+    _require_cuda_bf16(dout)
+    _require(out.dtype in (_BF16, torch.float32) and out.shape == dout.shape, "dsigmoid: bad out")
+    grad_pre = torch.empty(dout.shape, dtype=_BF16, device=dout.device)
+    _dsigmoid_out(out, dout, grad_pre)
+    return grad_pre
+
+
+def qknorm_rope_bwd(
+    dq: Tensor, dk: Tensor, dv: Optional[Tensor], x: Tensor, head_mean_sq: Tensor, gamma: Tensor, pos: Tensor, freq: Tensor,
+    head_dim: int, num_heads_q: int, num_heads_k: int, eps: float,
+) -> tuple[Tensor, Tensor]:
+    """Returns ``(grad, dgamma)``: ``grad = [grad_pre | dv]`` (bf16 ``[M, N]``) and fp32 ``dgamma[2*head_dim]``.
+
+    Counterpart of ``qknorm_rope_bwd`` (coda/core/elementwise/functional.py:421-456).
+    """
+    _require_cuda_bf16(dq, dk, x, gamma)
+    M, size_qk = x.shape
+    nv = dv.shape[1] if dv is not None else 0
+    grad = torch.empty(M, size_qk + nv, dtype=x.dtype, device=x.device)
+    dgamma = torch.empty(2 * head_dim, dtype=torch.float32, device=x.device)
+    nbytes = int(lib.coda_b200_qknorm_rope_bwd_scratch_bytes(M, head_dim))
+    scratch = torch.empty(nbytes // 4, dtype=torch.float32, device=x.device)
+    _qknorm_rope_bwd_out(
+        dq, dk, dv, x, head_mean_sq, gamma.contiguous(), pos.contiguous(), freq.contiguous(), head_dim, num_heads_q,
+        num_heads_k, float(eps), grad, dgamma, scratch,
+    )
+    return grad, dgamma

@@ -1,0 +1,172 @@
+"""Sharding of the fused-linear operators over the GPUs of one box (one process per GPU).
+
+The reference has no distributed code; this module adds what the operators
+need to run column-, head- or vocab-parallel over ``torch.distributed``:
+
+* ``linear_swiglu`` / ``linear_sigmoid``: column-parallel over the output
+  features (gate/up pairs stay together).  The forward needs no communication;
+  each rank's ``dx`` is a partial sum that :func:`allreduce_partial_dx` folds.
+* ``linear_qknorm_rope``: head-parallel (whole q heads, with the k and v heads
+  of their group).  ``dgamma`` is summed over ranks, ``dx`` as above.
+* ``linear_cross_entropy``: vocab-parallel.  Each rank runs the fused GEMM on
+  its vocabulary slice; one all-gather of per-row ``(lse, target logit)``
+  (8 bytes per row per rank) gives every rank the global log-sum-exp, and the
+  gradient pass uses it directly, so logits never exist anywhere.
+
+Host-side pieces (:func:`shard_bounds`, :func:`combine_lse`, the target
+re-basing) are plain tensor code and are exercised on CPU with the ``gloo``
+backend; the GEMMs and element-wise passes are the library's CUDA kernels.
+"""
+
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+import torch.distributed as dist
+from torch import Tensor
+
+
+def shard_bounds(total: int, rank: int, world: int, multiple: int = 1) -> tuple[int, int]:
+    """Contiguous slice ``[lo, hi)`` of ``total`` items for ``rank``, in units of ``multiple`` items.
+
+    The first ``(total / multiple) % world`` ranks get one extra unit, so any
+    ``total`` that is a multiple of ``multiple`` is covered without gaps.
+    """
+    if total % multiple != 0:
+        raise ValueError(f"{total} is not a multiple of {multiple}")
+    units = total // multiple
+    base, extra = divmod(units, world)
+    lo = rank * base + min(rank, extra)
+    hi = lo + base + (1 if rank < extra else 0)
+    return lo * multiple, hi * multiple
+
+
+def shard_swiglu_weight(weight: Tensor, rank: int, world: int) -> Tensor:
+    """Rows of the interleaved ``[2F, K]`` weight owned by ``rank``: whole (gate, up) pairs, 8 pairs at a time."""
+    lo, hi = shard_bounds(weight.shape[0], rank, world, multiple=16)
+    return weight[lo:hi]
+
+
+def shard_rows(weight: Tensor, rank: int, world: int, multiple: int = 8) -> Tensor:
+    """Output-feature rows ``[N/g]`` of a ``[N, K]`` weight owned by ``rank``."""
+    lo, hi = shard_bounds(weight.shape[0], rank, world, multiple=multiple)
+    return weight[lo:hi]
+
+
+def shard_qkv_weight(
+    weight: Tensor, frequencies: Tensor, head_dim: int, num_heads_q: int, num_heads_k: int, num_heads_v: int, rank: int, world: int
+) -> tuple[Tensor, Tensor, int, int, int]:
+    """Local ``[q_r | k_r | v_r]`` weight rows, the matching frequency slice and the local head counts."""
+    if num_heads_q % world or num_heads_k % world or num_heads_v % world:
+        raise ValueError("head counts must be divisible by the number of ranks")
+    d = head_dim
+    hq, hk, hv = num_heads_q // world, num_heads_k // world, num_heads_v // world
+    q0 = rank * hq * d
+    k0 = num_heads_q * d + rank * hk * d
+    v0 = (num_heads_q + num_heads_k) * d + rank * hv * d
+    local_w = torch.cat((weight[q0 : q0 + hq * d], weight[k0 : k0 + hk * d], weight[v0 : v0 + hv * d])).contiguous()
+    fq0 = rank * hq * d
+    fk0 = num_heads_q * d + rank * hk * d
+    local_f = torch.cat((frequencies[fq0 : fq0 + hq * d], frequencies[fk0 : fk0 + hk * d])).contiguous()
+    return local_w, local_f, hq, hk, hv
+
+
+def allreduce_partial_dx(dx: Tensor, group: Optional[dist.ProcessGroup] = None) -> Tensor:
+    """Sum the per-rank partial input gradients in place (bf16 on the wire, NCCL over NVLink)."""
+    if dist.is_initialized() and dist.get_world_size(group) > 1:
+        dist.all_reduce(dx, op=dist.ReduceOp.SUM, group=group)
+    return dx
+
+
+def rebase_target(target: Tensor, vocab_start: int, vocab_local: int, ignore_index: int) -> tuple[Tensor, int]:
+    """Targets in the index space of a vocabulary slice.
+
+    Rows whose label lives on another rank get a sentinel that matches no column
+    and differs from ``ignore_index``; ignored rows keep ``ignore_index``.
+    Returns ``(local_target, local_ignore_index)``.
+    """
+    sentinel = -1 if ignore_index != -1 else -2
+    local_ignore = ignore_index if ignore_index < 0 else -3  # keep the ignore marker outside [0, vocab_local)
+    local = target - vocab_start
+    owned = (local >= 0) & (local < vocab_local)
+    ignored = target == ignore_index
+    out = torch.where(owned, local, torch.full_like(local, sentinel))
+    out = torch.where(ignored, torch.full_like(local, local_ignore), out)
+    return out.to(dtype=torch.int32), local_ignore
+
+
+def combine_lse(local_lse: Tensor, local_target_logit: Tensor, group: Optional[dist.ProcessGroup] = None) -> tuple[Tensor, Tensor]:
+    """Global per-row ``(lse, target_logit)`` from each rank's slice values: one all-gather of ``[M, 2]`` fp32.
+
+    ``local_target_logit`` must be zero on ranks that do not own the row's label.
+    """
+    packed = torch.stack((local_lse, local_target_logit), dim=1).contiguous()
+    if dist.is_initialized() and dist.get_world_size(group) > 1:
+        world = dist.get_world_size(group)
+        gathered = torch.empty((world,) + tuple(packed.shape), dtype=packed.dtype, device=packed.device)
+        dist.all_gather(list(gathered.unbind(0)), packed, group=group)
+    else:
+        gathered = packed[None]
+    lse = torch.logsumexp(gathered[:, :, 0], dim=0)
+    target_logit = gathered[:, :, 1].sum(dim=0)
+    return lse, target_logit
+
+
+class VocabParallelLinearCrossEntropy(torch.autograd.Function):
+    """``linear_cross_entropy`` with ``weight`` sharded over the vocabulary; every rank returns the same loss."""
+
+    @staticmethod
+    def forward(ctx, x, weight_shard, target, vocab_start: int, ignore_index: int, reduction: str, group, reduce_dx: bool):
+        from . import ops
+
+        x = x.contiguous()
+        weight_shard = weight_shard.contiguous()
+        local_target, local_ignore = rebase_target(target, vocab_start, weight_shard.shape[0], ignore_index)
+        probs, part_max, part_sum, target_logit = ops.gemm_lse_partials(x, weight_shard.mT, local_target, store_probs=True)
+        local_lse, _ = ops.lse_finalize(part_max, part_sum, local_target, target_logit, local_ignore)
+        lse, tlogit = combine_lse(local_lse, target_logit, group)
+        valid = target != ignore_index
+        losses = torch.where(valid, lse - tlogit, torch.zeros_like(lse))
+        ops._ce_grad_fixup(probs, part_max, lse, local_target, int(local_ignore))
+        if reduction == "mean":
+            scale = 1.0 / valid.sum().float()
+            loss = losses.sum() * scale
+        else:
+            scale = None
+            loss = losses.sum()
+        ctx.save_for_backward(x, weight_shard, probs, scale)
+        ctx.group = group
+        ctx.reduce_dx = reduce_dx
+        return loss
+
+    @staticmethod
+    def backward(ctx, dloss):
+        from . import ops
+
+        x, weight_shard, dlogits, scale = ctx.saved_tensors
+        alpha = (dloss * scale if scale is not None else dloss).reshape(1).to(dtype=torch.float32)
+        dx = dweight = None
+        if ctx.needs_input_grad[0]:
+            dx = ops.gemm_scalar_scale(dlogits, weight_shard, alpha=alpha)
+            if ctx.reduce_dx:
+                allreduce_partial_dx(dx, ctx.group)
+        if ctx.needs_input_grad[1]:
+            dweight = ops.gemm_scalar_scale(dlogits.mT, x, alpha=alpha)
+        return dx, dweight, None, None, None, None, None, None
+
+
+def vocab_parallel_linear_cross_entropy(
+    x: Tensor,
+    weight_shard: Tensor,
+    target: Tensor,
+    vocab_start: int,
+    ignore_index: int = -100,
+    reduction: str = "mean",
+    group: Optional[dist.ProcessGroup] = None,
+    reduce_dx: bool = True,
+) -> Tensor:
+    """Loss of ``x @ W^T`` against ``target`` where this rank holds rows ``[vocab_start, vocab_start + len(shard))`` of ``W``."""
+    assert reduction in ("mean", "sum")
+    assert target.dtype == torch.int32
+    return VocabParallelLinearCrossEntropy.apply(x, weight_shard, target, vocab_start, ignore_index, reduction, group, reduce_dx)

@@ -1,0 +1,194 @@
+"""CPU/GPU-agnostic restatement of the reference's eager formulation of the hot path.
+
+TEST INFRASTRUCTURE ONLY.  Nothing under ``coda_kernels_b200/`` imports this
+module; it is the checker used by ``tests/``, by ``__graft_entry__.smoke()``
+and by the CPU-baseline / reference legs of ``bench.py``.
+
+Each function follows the PyTorch eager code the reference benchmarks use as
+their own ground truth (``benchmarks/backends/torch_linear.py`` over
+``benchmarks/backends/torch_ops.py``), evaluated as "fp32 math on the same bf16
+inputs": inputs are converted to ``compute_dtype`` (fp32 by default, fp64 for a
+tighter check) and all arithmetic, including the GEMM, runs in that type under
+autograd, so gradients come from ``torch.autograd.grad``.
+
+Pinning: the reference holds no golden vectors for this path.  This module is
+pinned against the reference's own eager implementation run in this build
+container; the vectors are committed under ``tests/golden/`` together with the
+script that produced them (``tests/golden/make_golden.py``), and
+``tests/test_oracle.py`` replays them.
+"""
+
+from __future__ import annotations
+
+import math
+
+import torch
+import torch.nn.functional as F
+
+
+def _c(t: torch.Tensor, dtype: torch.dtype) -> torch.Tensor:
+    return t.to(dtype=dtype)
+
+
+# ---------------------------------------------------------------------------------------------- swiglu
+def linear_swiglu(x: torch.Tensor, weight: torch.Tensor, compute_dtype: torch.dtype = torch.float32) -> torch.Tensor:
+    """``silu(gate) * up`` with gate/up interleaved along the rows of ``weight [2F, K]``.
+
+    Follows benchmarks/backends/torch_linear.py:19-33 and torch_ops.swiglu (torch_ops.py:18-32, interleaved layout).
+    """
+    preact = _c(x, compute_dtype) @ _c(weight, compute_dtype).mT
+    gate = preact[:, 0::2]
+    up = preact[:, 1::2]
+    return F.silu(gate) * up
+
+
+def dswiglu(preact: torch.Tensor, grad: torch.Tensor) -> torch.Tensor:
+    """Hand-written derivative of the interleaved SwiGLU (torch_ops.py:35-65)."""
+    gate = preact[:, 0::2]
+    up = preact[:, 1::2]
+    s = torch.sigmoid(gate)
+    silu = gate * s
+    dgate = grad * up * (s + silu * (1 - s))
+    dup = grad * silu
+    return torch.stack((dgate, dup), dim=-1).reshape(preact.shape)
+
+
+# ---------------------------------------------------------------------------------------------- sigmoid
+def linear_sigmoid(x: torch.Tensor, weight: torch.Tensor, compute_dtype: torch.dtype = torch.float32) -> torch.Tensor:
+    """``sigmoid(x @ weight^T)`` (benchmarks/backends/torch_linear.py:6-16, torch_ops.py:406-417)."""
+    return torch.sigmoid(_c(x, compute_dtype) @ _c(weight, compute_dtype).mT)
+
+
+# ---------------------------------------------------------------------------------------------- cross entropy
+def linear_cross_entropy(
+    x: torch.Tensor,
+    weight: torch.Tensor,
+    target: torch.Tensor,
+    ignore_index: int = -100,
+    reduction: str = "mean",
+    compute_dtype: torch.dtype = torch.float32,
+    chunk_rows: int = 1024,
+) -> torch.Tensor:
+    """Cross entropy of ``x @ weight^T`` (benchmarks/backends/torch_linear.py:83-104, torch_ops.py:1023-1037).
+
+    Rows are processed ``chunk_rows`` at a time so that the ``[rows, vocab]``
+    logits stay small, as the reference's oracle runner does
+    (benchmarks/utils/cases.py:20-24).  ``mean`` divides by the number of rows
+    whose target differs from ``ignore_index``.
+    """
+    assert reduction in ("mean", "sum")
+    w = _c(weight, compute_dtype)
+    total = None
+    for r0 in range(0, x.shape[0], chunk_rows):
+        logits = _c(x[r0 : r0 + chunk_rows], compute_dtype) @ w.mT
+        part = F.cross_entropy(logits, target[r0 : r0 + chunk_rows].long(), ignore_index=ignore_index, reduction="sum")
+        total = part if total is None else total + part
+    if reduction == "mean":
+        count = (target != ignore_index).sum().to(dtype=compute_dtype)
+        return total / count
+    return total
+
+
+def cross_entropy_rows(logits: torch.Tensor, target: torch.Tensor, ignore_index: int) -> tuple[torch.Tensor, torch.Tensor]:
+    """Per-row losses and ``softmax - onehot`` with ignored rows zeroed (torch_ops.py:279-313)."""
+    valid = target != ignore_index
+    safe = torch.where(valid, target, torch.zeros_like(target)).long()
+    rows = torch.arange(logits.shape[0], device=logits.device)
+    lse = torch.logsumexp(logits, dim=-1)
+    losses = torch.where(valid, lse - logits[rows, safe], torch.zeros_like(lse))
+    d = torch.softmax(logits, dim=-1)
+    d[rows, safe] -= 1
+    d = torch.where(valid[:, None], d, torch.zeros_like(d))
+    return losses, d
+
+
+# ---------------------------------------------------------------------------------------------- qk-norm + rope
+def rope_tables(positions: torch.Tensor, frequencies: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
+    """``cos``/``sin`` of ``2*pi * pos * (hi + lo)`` per rotary pair, formed in fp64 (torch_ops.py:116-132)."""
+    pairs = frequencies.to(dtype=torch.float64).reshape(-1, 2)
+    turns = pairs[:, 0] + pairs[:, 1]
+    angles = 2 * math.pi * positions.to(dtype=torch.float64)[:, None] * turns[None, :]
+    return torch.cos(angles), torch.sin(angles)
+
+
+def rope_interleaved(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> torch.Tensor:
+    """Rotate adjacent pairs ``(2p, 2p+1)``: ``(x0 c - x1 s, x1 c + x0 s)`` (torch_ops.py:148-196, interleaved layout).
+
+    ``cos``/``sin`` are ``[M, N/2]`` (one column per pair of ``x [M, N]``).
+    """
+    x0 = x[:, 0::2]
+    x1 = x[:, 1::2]
+    c = cos.to(dtype=x.dtype)
+    s = sin.to(dtype=x.dtype)
+    return torch.stack((x0 * c - x1 * s, x1 * c + x0 * s), dim=-1).reshape(x.shape)
+
+
+def head_mean_square(x: torch.Tensor, head_dim: int) -> torch.Tensor:
+    """``[M, heads]`` mean of squares per head (torch_ops.py:199-206)."""
+    return x.reshape(x.shape[0], -1, head_dim).square().mean(dim=-1)
+
+
+def qknorm(x, head_mean_sq, gamma, head_dim, num_heads_q, num_heads_k, eps):
+    """Each head times ``rsqrt(mean_sq + eps)`` and its gamma (q heads: ``gamma[:d]``, k heads: ``gamma[d:]``); torch_ops.py:209-230."""
+    xh = x.reshape(x.shape[0], -1, head_dim)
+    rstd = torch.rsqrt(head_mean_sq + eps)[..., None]
+    gq, gk = gamma[:head_dim], gamma[head_dim:]
+    g = torch.cat((gq.expand(num_heads_q, head_dim), gk.expand(num_heads_k, head_dim)))
+    return (xh * rstd * g).reshape(x.shape)
+
+
+def linear_qknorm_rope(
+    x, weight, gamma, positions, frequencies, head_dim, num_heads_q, num_heads_k, eps, compute_dtype=torch.float32
+):
+    """``(q, k, v)`` of the fused projection (benchmarks/backends/torch_linear.py:36-80, torch_ops.py:675-722)."""
+    size_q = head_dim * num_heads_q
+    size_qk = head_dim * (num_heads_q + num_heads_k)
+    xc = _c(x, compute_dtype)
+    wc = _c(weight, compute_dtype)
+    preact = xc @ wc[:size_qk].mT
+    ms = head_mean_square(preact, head_dim)
+    normed = qknorm(preact, ms, _c(gamma, compute_dtype), head_dim, num_heads_q, num_heads_k, eps)
+    cos, sin = rope_tables(positions, frequencies)
+    rotated = rope_interleaved(normed, cos, sin)
+    v = xc @ wc[size_qk:].mT
+    return rotated[:, :size_q], rotated[:, size_q:], v
+
+
+# ---------------------------------------------------------------------------------------------- fwd + bwd helpers
+def fwd_bwd(fn, inputs: dict, grad_names: list[str], cotangents):
+    """Run ``fn(**inputs)`` with autograd on ``grad_names`` and return ``(outputs, grads)``.
+
+    ``cotangents`` is one tensor or a tuple matching ``fn``'s outputs; they are cast to the outputs' dtype.
+    """
+    work = dict(inputs)
+    leaves = []
+    for name in grad_names:
+        leaf = work[name].detach().clone().to(dtype=torch.float32 if work[name].dtype != torch.float64 else torch.float64)
+        leaf.requires_grad_(True)
+        work[name] = leaf
+        leaves.append(leaf)
+    out = fn(**work)
+    outs = out if isinstance(out, tuple) else (out,)
+    cots = cotangents if isinstance(cotangents, tuple) else (cotangents,)
+    cots = tuple(c.to(dtype=o.dtype) for c, o in zip(cots, outs))
+    grads = torch.autograd.grad(outs, leaves, cots)
+    return tuple(o.detach() for o in outs), dict(zip(grad_names, grads))
+
+
+# ---------------------------------------------------------------------------------------------- error metrics
+def max_rel_err(a: torch.Tensor, b: torch.Tensor) -> float:
+    """``max|a - b| / max|b|``: the tolerance metric of the parity tests (b = oracle)."""
+    a = a.detach().to(dtype=torch.float64, device="cpu")
+    b = b.detach().to(dtype=torch.float64, device="cpu")
+    denom = b.abs().max().item()
+    if denom == 0.0:
+        return float((a - b).abs().max().item())
+    return float((a - b).abs().max().item() / denom)
+
+
+def rel_l2_err(a: torch.Tensor, b: torch.Tensor) -> float:
+    """``||a - b|| / ||b||``: the metric the reference's harness reports (benchmarks/utils/numerics.py:20-29)."""
+    a = a.detach().to(dtype=torch.float64, device="cpu")
+    b = b.detach().to(dtype=torch.float64, device="cpu")
+    denom = b.norm().item()
+    return float((a - b).norm().item() / denom) if denom != 0.0 else float((a - b).norm().item())

@@ -1,0 +1,104 @@
+"""Generates the golden vectors under tests/golden/ from the reference's own eager implementation.
+
+Run in a container where the reference tree is mounted (default /root/reference):
+
+    python tests/golden/make_golden.py [/path/to/reference]
+
+It imports ``benchmarks/backends/torch_linear.py`` and ``torch_ops.py`` of the
+reference unmodified, evaluates every operator of the hot path forward and
+backward in fp64 on small seeded bf16 inputs, and stores inputs, outputs and
+gradients in one ``.pt`` file per case.  The files are small (tens of KB) and
+are committed; the reference itself is never copied.
+"""
+
+from __future__ import annotations
+
+import sys
+from pathlib import Path
+
+import torch
+
+HERE = Path(__file__).resolve().parent
+REPO = HERE.parent.parent
+REF = Path(sys.argv[1]) if len(sys.argv) > 1 else Path("/root/reference")
+sys.path.insert(0, str(REF))
+sys.path.insert(0, str(REPO))
+
+from benchmarks.backends import torch_linear, torch_ops  # noqa: E402  (reference code)
+
+from oracle import inputs as synth  # noqa: E402
+
+F64 = torch.float64
+IL = torch_ops.PairLayout.interleaved
+
+
+def leaf(t):
+    return t.detach().to(dtype=F64).requires_grad_(True)
+
+
+def save(name, payload):
+    torch.save(payload, HERE / f"{name}.pt")
+    print(f"wrote {name}.pt")
+
+
+def swiglu_case(name, M, K, Fdim, seed):
+    d = synth.swiglu_inputs(M, K, Fdim, seed)
+    x, w = leaf(d["x"]), leaf(d["weight"])
+    out = torch_linear.linear_swiglu(x, w, layout=IL)
+    dx, dw = torch.autograd.grad(out, (x, w), d["dout"].to(F64))
+    preact = (x @ w.mT).detach()
+    dpre, post = torch_ops.dswiglu(preact, d["dout"].to(F64), IL)
+    save(name, {"inputs": d, "out": out.detach(), "dx": dx, "dweight": dw, "preact": preact, "dpreact": dpre, "postact": post})
+
+
+def sigmoid_case(name, M, K, N, seed):
+    d = synth.sigmoid_inputs(M, K, N, seed)
+    x, w = leaf(d["x"]), leaf(d["weight"])
+    out = torch_linear.linear_sigmoid(x, w)
+    dx, dw = torch.autograd.grad(out, (x, w), d["dout"].to(F64))
+    save(name, {"inputs": d, "out": out.detach(), "dx": dx, "dweight": dw})
+
+
+def ce_case(name, M, K, V, seed, reduction, ignore_frac):
+    d = synth.cross_entropy_inputs(M, K, V, seed, ignore_frac=ignore_frac)
+    x, w = leaf(d["x"]), leaf(d["weight"])
+    tgt = d["target"].long()
+    loss = torch_linear.linear_cross_entropy(x, w, tgt, logits_dtype=F64, ignore_index=-100, reduction=reduction)
+    dx, dw = torch.autograd.grad(loss, (x, w))
+    logits = (x @ w.mT).detach()
+    losses, dlogits = torch_ops.cross_entropy(logits, tgt, -100)
+    margins, lses, tlog = torch_ops.gemm_lse_select_logits(x.detach(), w.detach().mT, tgt, -100, logits_dtype=F64)
+    save(name, {"inputs": d, "reduction": reduction, "loss": loss.detach(), "dx": dx, "dweight": dw, "row_losses": losses,
+                "dlogits": dlogits, "select_losses": margins, "lse": lses, "target_logit": tlog})
+
+
+def qk_case(name, M, K, d_, hq, hk, hv, seq, seed, pos_offset, float_pos=False):
+    d = synth.qknorm_rope_inputs(M, K, d_, hq, hk, hv, seq, seed=seed, pos_offset=pos_offset)
+    if float_pos:
+        d["positions"] = d["positions"].to(torch.float32)
+    x, w, g = leaf(d["x"]), leaf(d["weight"]), leaf(d["gamma"])
+    freq = d["frequencies"].to(F64)
+    pos = d["positions"].to(F64)
+    q, k, v = torch_linear.linear_qknorm_rope(x, w, g, cos=None, sin=None, positions=pos, frequencies=freq, head_dim=d_,
+                                              num_heads_q=hq, num_heads_k=hk, eps=1e-6, layout=IL)
+    dx, dw, dg = torch.autograd.grad((q, k, v), (x, w, g), (d["dq"].to(F64), d["dk"].to(F64), d["dv"].to(F64)))
+    size_qk = (hq + hk) * d_
+    preact = (x @ w[:size_qk].mT).detach()
+    ms = torch_ops.head_mean_square(preact, d_)
+    gpre, dgam = torch_ops.qknorm_rope_bwd(d["dq"].to(F64), d["dk"].to(F64), preact, ms, g.detach(), cos=None, sin=None, pos=pos,
+                                           freq=freq, head_dim=d_, num_heads_q=hq, num_heads_k=hk, eps=1e-6, layout=IL)
+    save(name, {"inputs": d, "cfg": {"head_dim": d_, "hq": hq, "hk": hk, "hv": hv, "eps": 1e-6}, "q": q.detach(), "k": k.detach(),
+                "v": v.detach(), "dx": dx, "dweight": dw, "dgamma": dg, "preact": preact, "mean_sq": ms, "grad_pre": gpre,
+                "dgamma_bwd": dgam})
+
+
+if __name__ == "__main__":
+    torch.manual_seed(0)
+    swiglu_case("swiglu_small", 48, 64, 40, seed=1)
+    swiglu_case("swiglu_ragged", 37, 72, 24, seed=2)
+    sigmoid_case("sigmoid_small", 40, 64, 48, seed=3)
+    ce_case("ce_mean", 40, 64, 304, seed=4, reduction="mean", ignore_frac=0.2)
+    ce_case("ce_sum", 33, 72, 520, seed=5, reduction="sum", ignore_frac=0.1)
+    qk_case("qk_gqa_d64", 24, 64, 64, 4, 2, 2, seq=12, seed=6, pos_offset=0)
+    qk_case("qk_gqa_d128_far", 20, 72, 128, 2, 1, 1, seq=10, seed=7, pos_offset=1 << 20)
+    qk_case("qk_mha_d64_fpos", 16, 64, 64, 2, 2, 2, seq=16, seed=8, pos_offset=5, float_pos=True)

@@ -1,0 +1,97 @@
+"""Host-side logic: RoPE frequency tables, shard bounds, target re-basing, and the 2-rank LSE exchange over gloo."""
+
+import math
+import os
+import socket
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from coda_kernels_b200 import parallel, rope_utils
+from oracle import eager, inputs
+
+
+def test_make_rope_frequencies_contract():
+    inv = rope_utils.rope_inv_freq(128, theta=500000.0)
+    f = rope_utils.make_rope_frequencies(inv, num_heads=5)
+    assert f.dtype == torch.float32 and f.shape == (5 * 128,)
+    pairs = f[:128].reshape(-1, 2).to(torch.float64)
+    turns = inv.to(torch.float64) / (2 * math.pi)
+    assert torch.allclose(pairs.sum(dim=1), turns, rtol=1e-13, atol=0)
+    assert torch.equal(f[:128], f[128:256])
+    # same table as the synthetic-input generator of the oracle
+    d = inputs.qknorm_rope_inputs(4, 16, 128, 3, 2, 2, 4)
+    assert torch.equal(d["frequencies"], f)
+
+
+def test_shard_bounds_cover_everything():
+    for total, world, mult in [(28672, 8, 16), (128256, 8, 8), (5120, 4, 8), (48, 5, 16)]:
+        spans = [parallel.shard_bounds(total, r, world, mult) for r in range(world)]
+        assert spans[0][0] == 0 and spans[-1][1] == total
+        for (a, b), (c, d) in zip(spans, spans[1:]):
+            assert b == c and (b - a) % mult == 0
+    with pytest.raises(ValueError):
+        parallel.shard_bounds(100, 0, 2, 16)
+
+
+def test_shard_qkv_weight_layout():
+    d, hq, hk, hv, K = 4, 4, 2, 2, 3
+    w = torch.arange((hq + hk + hv) * d * K, dtype=torch.float32).reshape(-1, K)
+    f = torch.arange((hq + hk) * d, dtype=torch.float32)
+    lw, lf, lq, lk, lv = parallel.shard_qkv_weight(w, f, d, hq, hk, hv, rank=1, world=2)
+    assert (lq, lk, lv) == (2, 1, 1)
+    assert torch.equal(lw[: 2 * d], w[2 * d : 4 * d])
+    assert torch.equal(lw[2 * d : 3 * d], w[hq * d + d : hq * d + 2 * d])
+    assert torch.equal(lw[3 * d :], w[(hq + hk) * d + d : (hq + hk) * d + 2 * d])
+    assert torch.equal(lf, torch.cat((f[2 * d : 4 * d], f[hq * d + d : hq * d + 2 * d])))
+
+
+def test_rebase_target():
+    t = torch.tensor([0, 5, 9, -100, 10, 19], dtype=torch.int32)
+    local, ign = parallel.rebase_target(t, vocab_start=10, vocab_local=10, ignore_index=-100)
+    assert ign == -100
+    assert local.tolist() == [-1, -1, -1, -100, 0, 9]
+    local, ign = parallel.rebase_target(torch.tensor([0, 3, 12], dtype=torch.int32), 10, 10, ignore_index=0)
+    assert ign == -3 and local.tolist() == [-3, -1, 2]
+
+
+def _free_port() -> int:
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _lse_worker(rank: int, world: int, port: int, result_path: str):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        d = inputs.cross_entropy_inputs(24, 32, 80, seed=11, ignore_frac=0.25)
+        x, w, t = d["x"].float(), d["weight"].float(), d["target"]
+        lo, hi = parallel.shard_bounds(w.shape[0], rank, world, 8)
+        logits = x @ w[lo:hi].T
+        local_t, ign = parallel.rebase_target(t, lo, hi - lo, -100)
+        local_lse = torch.logsumexp(logits, dim=1)
+        owned = local_t >= 0
+        tl = torch.where(owned, logits[torch.arange(24), local_t.clamp(min=0).long()], torch.zeros(24))
+        lse, tlogit = parallel.combine_lse(local_lse, tl)
+        valid = t != -100
+        losses = torch.where(valid, lse - tlogit, torch.zeros_like(lse))
+        loss = losses.sum() / valid.sum()
+        ref = eager.linear_cross_entropy(d["x"], d["weight"], t)
+        dx_partial = torch.full((4, 4), float(rank + 1))
+        parallel.allreduce_partial_dx(dx_partial)
+        ok = abs(loss.item() - ref.item()) < 1e-5 and torch.equal(dx_partial, torch.full((4, 4), 3.0))
+        if rank == 0:
+            with open(result_path, "w") as f:
+                f.write(f"{int(ok)} {loss.item()} {ref.item()}")
+    finally:
+        dist.destroy_process_group()
+
+
+def test_vocab_parallel_lse_exchange_two_ranks(tmp_path):
+    out = tmp_path / "result.txt"
+    mp.spawn(_lse_worker, args=(2, _free_port(), str(out)), nprocs=2, join=True)
+    ok, loss, ref = out.read_text().split()
+    assert ok == "1", f"sharded loss {loss} vs oracle {ref}"
