@@ -316,7 +316,7 @@ def workload_name(op: str) -> str:
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--op", default="swiglu", choices=list(SHAPES))
@@ -432,10 +432,10 @@ def main() -> None:
     # ---- CPU baseline (rank 0, single GPU run only)
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
-        rows = args.cpu_rows or 1024
-        tf, dt = time_cpu(args.op, rows, steps=2, warmup=1)
+        rows = args.cpu_rows or 4096
+        tf, dt = time_cpu(args.op, rows, steps=3, warmup=1)
         cpu = {"value": tf, "unit": "TFLOP/s", "cores": torch.get_num_threads(), "kind": "port", "seconds_per_sample_step": dt,
-               "sample": f"rows 0..{rows - 1} of {SHAPES[args.op]['M']} (full K and output width), fwd+bwd, 1 warm-up + 2 timed"}
+               "sample": f"rows 0..{rows - 1} of {SHAPES[args.op]['M']} (full K and output width), fwd+bwd, 1 warm-up + 3 timed"}
 
     if rank == 0:
         s = SHAPES[args.op]
