@@ -139,13 +139,15 @@ class ClockSampler:
 class Workload:
     """One operator at its benchmark shape, sharded for ``world`` ranks; inputs live on ``device``."""
 
-    def __init__(self, op: str, rank: int, world: int, device: torch.device, pinned_host: bool):
+    def __init__(self, op: str, rank: int, world: int, device: torch.device, pinned_host: bool, rows: int = 0):
         import coda_kernels_b200 as ck
         from coda_kernels_b200 import parallel
         from oracle import inputs
 
         self.op, self.rank, self.world, self.device, self.ck, self.parallel = op, rank, world, device, ck, parallel
-        s = SHAPES[op]
+        s = dict(SHAPES[op])
+        if rows:
+            s["M"] = rows  # reduced-row variant of the same workload (profiling captures)
         self.shape = s
         if op == "swiglu":
             d = inputs.swiglu_inputs(s["M"], s["K"], s["F"])
@@ -321,6 +323,7 @@ def main() -> None:
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--op", default="swiglu", choices=list(SHAPES))
     ap.add_argument("--cpu-rows", type=int, default=0, help="rows of the CPU-baseline sample (0 = default)")
+    ap.add_argument("--rows", type=int, default=0, help="override the number of rows M (small captures under ncu); 0 = benchmark shape")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--reduce-dx", action="store_true", help="all-reduce the partial dx over ranks inside the step")
@@ -348,7 +351,7 @@ def main() -> None:
             torch.distributed.barrier()
         torch.cuda.synchronize()
 
-    wl = Workload(args.op, rank, world, device, pinned_host=not args.no_e2e)
+    wl = Workload(args.op, rank, world, device, pinned_host=not args.no_e2e, rows=args.rows)
     from coda_kernels_b200 import ops, parallel
 
     def full_step():
@@ -379,7 +382,7 @@ def main() -> None:
     if world > 1:
         torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
     ms_step = float(t.item()) / args.steps
-    flops = algorithmic_flops(args.op, SHAPES[args.op])
+    flops = algorithmic_flops(args.op, wl.shape)
     value = flops / (ms_step * 1e-3) / 1e12
 
     # ---- end to end: host buffers in, host buffers out, every step
@@ -438,12 +441,12 @@ def main() -> None:
                "sample": f"rows 0..{rows - 1} of {SHAPES[args.op]['M']} (full K and output width), fwd+bwd, 1 warm-up + 3 timed"}
 
     if rank == 0:
-        s = SHAPES[args.op]
+        s = wl.shape
         line = {
             "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
             "data": "synthetic",
-            "config": {"workload": workload_name(args.op), **s, "global_batch_tokens": s["M"],
+            "config": {"workload": workload_name(args.op) + (f" [rows reduced to {args.rows}]" if args.rows else ""), **s, "global_batch_tokens": s["M"],
                        "parallelism": {"swiglu": "column", "sigmoid": "column", "cross_entropy": "vocab", "qknorm_rope": "head"}[args.op] + f"-parallel x{world}",
                        "dx_allreduce": bool(args.reduce_dx and world > 1),
                        "l2": f"no flush: each step streams {wl.h2d_bytes / 1e6:.0f} MB of inputs plus larger intermediates, above the 126 MB L2"},
