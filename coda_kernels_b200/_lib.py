@@ -43,6 +43,10 @@ SIGNATURES = {
         _I,
         [_P, _L, _P, _L, _P, _L, _I, _P, _L, _P, _P, _P, _I, _P, _I, _I, _I, _F, _P, _L, _P, _P, _L, _I, _P],
     ),
+    "coda_b200_qknorm_rope_bwd_noalloc": (
+        _I,
+        [_P, _L, _P, _L, _P, _L, _I, _P, _L, _P, _P, _P, _I, _P, _I, _I, _I, _F, _P, _L, _P, _I, _P],
+    ),
 }
 
 

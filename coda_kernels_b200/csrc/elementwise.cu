@@ -400,3 +400,54 @@ extern "C" int coda_b200_qknorm_rope_bwd(const void* dq, int64_t ld_dq, const vo
   fold_partials_kernel<<<(2 * head_dim + 255) / 256, 256, 0, st>>>(partials, blocks, 2 * head_dim, dgamma);
   return launch_check("fold_partials launch");
 }
+
+// ------------------------------------------------------------------ QK-norm + RoPE backward without a caller-provided workspace
+// Some hosts cannot give this library a scratch buffer: a plain C or ctypes
+// caller that owns nothing but its input and output arrays, or a process that
+// reserved all device memory at start-up and forbids cudaMalloc afterwards
+// (cudaMalloc synchronises the device and may fail late under memory pressure).
+// For them the per-block partial sums of dgamma live in this fixed array, which
+// every GPU that loads the library keeps resident until the process exits.
+constexpr int kNoAllocMaxRows = 16384;                                                // largest M accepted
+constexpr int kNoAllocMaxBlocks = (kNoAllocMaxRows + kQkRowsPerBlock - 1) / kQkRowsPerBlock;  // 1024 partial rows
+constexpr int kNoAllocScratchFloats = kNoAllocMaxBlocks * 2 * 128;                    // 1 MiB of fp32
+static __device__ __align__(256) float g_qk_bwd_scratch[kNoAllocScratchFloats];
+
+namespace {
+// Device address of g_qk_bwd_scratch on the current device.  In host code the
+// array's name is only a handle for the runtime, never a pointer a kernel may
+// dereference, so the address is looked up once per device and cached.
+int noalloc_scratch_ptr(float** out) {
+  static float* cached[64] = {nullptr};
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return fail(kCudaError, std::string("cudaGetDevice: ") + cudaGetErrorString(e));
+  if (dev < 0 || dev >= 64) return fail(kBadArgument, "device ordinal out of range for the built-in scratch table");
+  if (cached[dev] == nullptr) {
+    void* p = nullptr;
+    e = cudaGetSymbolAddress(&p, g_qk_bwd_scratch);
+    if (e != cudaSuccess || p == nullptr)
+      return fail(kCudaError, std::string("cudaGetSymbolAddress(g_qk_bwd_scratch): ") + cudaGetErrorString(e));
+    cached[dev] = static_cast<float*>(p);
+  }
+  *out = cached[dev];
+  return kOk;
+}
+}  // namespace
+
+extern "C" int coda_b200_qknorm_rope_bwd_noalloc(const void* dq, int64_t ld_dq, const void* dk, int64_t ld_dk, const void* dv,
+                                                 int64_t ld_dv, int nv, const void* preact, int64_t ld_pre,
+                                                 const float* mean_sq, const void* gamma, const void* positions,
+                                                 int pos_is_float, const float* frequencies, int head_dim, int hq, int hk,
+                                                 float eps, void* grad, int64_t ld_grad, float* dgamma, int M, void* stream) {
+  if (M > kNoAllocMaxRows)
+    return fail(kBadArgument, "coda_b200_qknorm_rope_bwd_noalloc handles at most " + std::to_string(kNoAllocMaxRows) +
+                                  " rows per call (got " + std::to_string(M) + "); split the batch or use coda_b200_qknorm_rope_bwd");
+  if (head_dim != 64 && head_dim != 128) return fail(kBadArgument, "head_dim must be 64 or 128");
+  float* scratch = nullptr;
+  const int rc = noalloc_scratch_ptr(&scratch);
+  if (rc != kOk) return rc;
+  return coda_b200_qknorm_rope_bwd(dq, ld_dq, dk, ld_dk, dv, ld_dv, nv, preact, ld_pre, mean_sq, gamma, positions, pos_is_float,
+                                   frequencies, head_dim, hq, hk, eps, grad, ld_grad, dgamma, scratch,
+                                   static_cast<int64_t>(sizeof(float)) * kNoAllocScratchFloats, M, stream);
+}

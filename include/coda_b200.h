@@ -138,6 +138,26 @@ int coda_b200_qknorm_rope_bwd(const void* dq, int64_t ld_dq, const void* dk, int
                               int hk, float eps, void* grad, int64_t ld_grad, float* dgamma, void* scratch,
                               int64_t scratch_bytes, int M, void* stream);
 
+/* Same computation and arguments as coda_b200_qknorm_rope_bwd, minus the
+ * scratch buffer.  This entry point has no counterpart in the reference; it
+ * exists for hosts that cannot supply a workspace: a bare C / ctypes caller
+ * that owns only its input and output arrays, or a process that took all of
+ * its device memory at start-up and may not call cudaMalloc afterwards.  The
+ * per-block dgamma partials go to a 1 MiB array built into the library (held by
+ * every GPU that loads it until the process exits), so
+ *   - M may be at most 16384 rows per call; larger M returns CODA_B200_EARG;
+ *   - it calls no cudaMalloc / cudaFree or any other allocating routine;
+ *   - the first call on each device looks up the array's device address (with
+ *     that device current); make that first call before any stream capture;
+ *   - all calls share the array, which keeps the previous call's contents (each
+ *     call overwrites every entry it later reads, so nothing needs clearing);
+ *     two calls that overlap on the GPU (different streams) race on it. */
+int coda_b200_qknorm_rope_bwd_noalloc(const void* dq, int64_t ld_dq, const void* dk, int64_t ld_dk, const void* dv,
+                                      int64_t ld_dv, int nv, const void* preact, int64_t ld_pre, const float* mean_sq,
+                                      const void* gamma, const void* positions, int pos_is_float, const float* frequencies,
+                                      int head_dim, int hq, int hk, float eps, void* grad, int64_t ld_grad, float* dgamma,
+                                      int M, void* stream);
+
 #ifdef __cplusplus
 }
 #endif
