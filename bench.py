@@ -48,6 +48,12 @@ SHAPES = {
 }
 
 
+# DRAM bytes per launch of the dominant kernel (dram__bytes_read.sum + dram__bytes_write.sum from one ncu capture).
+# swiglu: 866.9 MB measured at 4096 rows (profiles/gemm_kernels_swiglu_rows4096.md), x4 for the 16384-row launch,
+# since the traffic grows in proportion to the rows.
+NCU_TRAFFIC = {"swiglu": 3.467e9}
+
+
 def algorithmic_flops(op: str, s: dict) -> float:
     """Forward + backward GEMM flops (3 GEMMs of 2*M*K*N each); recomputation never counts."""
     if op == "swiglu":
@@ -84,7 +90,9 @@ class ClockSampler:
         self.proc = None
         self.thread = None
 
-    def start(self):
+    def start(self, wait_s: float = 8.0):
+        """Launch nvidia-smi and wait for its first sample: its start-up stalls CUDA launches for a while, so it
+        has to be over before anything is timed."""
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", "-i", str(self.gpu_index), f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100"],
@@ -94,6 +102,12 @@ class ClockSampler:
             return
         self.thread = threading.Thread(target=self._read, daemon=True)
         self.thread.start()
+        t0 = time.perf_counter()
+        while not self.rows and time.perf_counter() - t0 < wait_s:
+            time.sleep(0.05)
+
+    def mark(self) -> int:
+        return len(self.rows)
 
     def _read(self):
         for line in self.proc.stdout:
@@ -101,7 +115,8 @@ class ClockSampler:
             if len(parts) == 7:
                 self.rows.append(parts)
 
-    def stop(self) -> dict:
+    def stop(self, first: int = 0, last: int | None = None) -> dict:
+        """Stop sampling; summarise the samples taken between the two marks (the timed region)."""
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
         self.proc.terminate()
@@ -115,7 +130,10 @@ class ClockSampler:
         reasons = set()
         sm_max = None
         power = []
-        for r in self.rows:
+        rows = self.rows[first:last] if (last is not None and last > first) else self.rows[first:]
+        if not rows:
+            rows = self.rows[-1:]
+        for r in rows:
             try:
                 sm.append(float(r[0]))
                 sm_max = float(r[1])
@@ -125,7 +143,6 @@ class ClockSampler:
             for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), r[3:7]):
                 if val.lower().startswith("active"):
                     reasons.add(name)
-        # samples under load = upper half of the observed clocks' time span (idle samples bracket the region)
         return {
             "sm_mhz": statistics.median(sm) if sm else None,
             "sm_max_mhz": sm_max,
@@ -326,6 +343,7 @@ def main() -> None:
     ap.add_argument("--rows", type=int, default=0, help="override the number of rows M (small captures under ncu); 0 = benchmark shape")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-clocks", action="store_true", help="do not sample nvidia-smi during the timed region")
     ap.add_argument("--reduce-dx", action="store_true", help="all-reduce the partial dx over ranks inside the step")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
@@ -344,6 +362,7 @@ def main() -> None:
     torch.cuda.set_device(device)
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")  # keep NCCL's banner off stdout: rank 0 prints one JSON line there
         torch.distributed.init_process_group("nccl", device_id=device)
 
     def barrier():
@@ -361,22 +380,22 @@ def main() -> None:
         return res
 
     # ---- device-resident timing
+    sampler = ClockSampler(local_rank)
+    if rank == 0 and not args.no_clocks:
+        sampler.start()
     for _ in range(args.warmup):
         full_step()
     barrier()
-    sampler = ClockSampler(local_rank)
-    if rank == 0:
-        sampler.start()
-        time.sleep(0.3)
-    barrier()
+    mark0 = sampler.mark()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     for _ in range(args.steps):
         res = full_step()
     e1.record()
     barrier()
+    mark1 = sampler.mark()
     ms_total = e0.elapsed_time(e1)
-    clocks = sampler.stop() if rank == 0 else None
+    clocks = sampler.stop(mark0, mark1) if (rank == 0 and not args.no_clocks) else None
     ops.check_device_status(device)
     t = torch.tensor([ms_total], device=device)
     if world > 1:
@@ -421,13 +440,7 @@ def main() -> None:
     k_ms = e0.elapsed_time(e1) / n_k
     achieved = k_flops / (k_ms * 1e-3) / 1e12
     peak = float(peaks.get("bf16_tflops", FALLBACK_PEAKS["bf16_tflops"]))
-    traffic_path = REPO / "profiles" / f"traffic_{args.op}.json"
-    traffic = None
-    if traffic_path.exists():
-        try:
-            traffic = json.loads(traffic_path.read_text()).get("dram_bytes_per_launch")
-        except Exception:
-            traffic = None
+    traffic = NCU_TRAFFIC.get(args.op) if (world == 1 and not args.rows) else None
     roofline = {"bound": "tensor", "kernel": label, "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
                 "peak_kind": f"{peak_kind} burst bf16 (kernel timed alone)", "ms_per_launch": k_ms, "flops_per_launch": k_flops,
                 "traffic": traffic}

@@ -278,13 +278,24 @@ qknorm_rope_bwd_kernel(const __nv_bfloat16* __restrict__ dq, long long ld_dq, co
   }
 }
 
+// Column sums of the [nblocks, width] partials: 32 columns x 8 row-lanes per block, rows strided over the lanes.
 __global__ void __launch_bounds__(256) fold_partials_kernel(const float* __restrict__ partials, int nblocks, int width,
                                                             float* __restrict__ out) {
-  const int c = blockIdx.x * blockDim.x + threadIdx.x;
-  if (c >= width) return;
+  __shared__ float red[8][33];
+  const int cx = threadIdx.x & 31, ry = threadIdx.x >> 5;
+  const int c = blockIdx.x * 32 + cx;
   float s = 0.f;
-  for (int b = 0; b < nblocks; ++b) s += partials[static_cast<long long>(b) * width + c];
-  out[c] = s;
+  if (c < width) {
+    for (int b = ry; b < nblocks; b += 8) s += partials[static_cast<long long>(b) * width + c];
+  }
+  red[ry][cx] = s;
+  __syncthreads();
+  if (ry == 0 && c < width) {
+    float t = 0.f;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) t += red[j][cx];
+    out[c] = t;
+  }
 }
 
 inline int grid_for(long long total, int block) {
@@ -397,7 +408,7 @@ extern "C" int coda_b200_qknorm_rope_bwd(const void* dq, int64_t ld_dq, const vo
         static_cast<__nv_bfloat16*>(grad), ld_grad, partials, M);
   int rc = launch_check("qknorm_rope_bwd launch");
   if (rc != kOk) return rc;
-  fold_partials_kernel<<<(2 * head_dim + 255) / 256, 256, 0, st>>>(partials, blocks, 2 * head_dim, dgamma);
+  fold_partials_kernel<<<(2 * head_dim + 31) / 32, 256, 0, st>>>(partials, blocks, 2 * head_dim, dgamma);
   return launch_check("fold_partials launch");
 }
 
