@@ -177,18 +177,18 @@ def fwd_bwd(fn, inputs: dict, grad_names: list[str], cotangents):
 
 # ---------------------------------------------------------------------------------------------- error metrics
 def max_rel_err(a: torch.Tensor, b: torch.Tensor) -> float:
-    """``max|a - b| / max|b|``: the tolerance metric of the parity tests (b = oracle)."""
-    a = a.detach().to(dtype=torch.float64, device="cpu")
-    b = b.detach().to(dtype=torch.float64, device="cpu")
+    """``max|a - b| / max|b|``: the tolerance metric of the parity tests (b = oracle).  Evaluated where ``b`` lives."""
+    a = a.detach().to(device=b.device, dtype=torch.float64)
+    b = b.detach().to(dtype=torch.float64)
     denom = b.abs().max().item()
-    if denom == 0.0:
-        return float((a - b).abs().max().item())
-    return float((a - b).abs().max().item() / denom)
+    num = (a - b).abs().max().item()
+    return float(num) if denom == 0.0 else float(num / denom)
 
 
 def rel_l2_err(a: torch.Tensor, b: torch.Tensor) -> float:
     """``||a - b|| / ||b||``: the metric the reference's harness reports (benchmarks/utils/numerics.py:20-29)."""
-    a = a.detach().to(dtype=torch.float64, device="cpu")
-    b = b.detach().to(dtype=torch.float64, device="cpu")
+    a = a.detach().to(device=b.device, dtype=torch.float64)
+    b = b.detach().to(dtype=torch.float64)
     denom = b.norm().item()
-    return float((a - b).norm().item() / denom) if denom != 0.0 else float((a - b).norm().item())
+    num = (a - b).norm().item()
+    return float(num) if denom == 0.0 else float(num / denom)
