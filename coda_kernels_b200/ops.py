@@ -269,8 +269,15 @@ def gemm_swiglu(A: Tensor, B: Tensor) -> tuple[Tensor, Tensor]:
     return preact, postact
 
 
+# Tiling constants of the library, read once at import so that the wrappers below are plain Python arithmetic
+# (traceable by torch.compile, which cannot look into ctypes calls).
+_LSE_TILE_N = (1 << 20) // int(lib.coda_b200_lse_tiles(1 << 20))
+_QK_BWD_ROWS_PER_BLOCK = (1 << 20) * 2 * 128 * 4 // int(lib.coda_b200_qknorm_rope_bwd_scratch_bytes(1 << 20, 128))
+
+
 def lse_tiles(N: int) -> int:
-    return int(lib.coda_b200_lse_tiles(int(N)))
+    """Number of column tiles of the LSE epilogue (= ``coda_b200_lse_tiles(N)``)."""
+    return (N + _LSE_TILE_N - 1) // _LSE_TILE_N
 
 
 def gemm_lse_partials(A: Tensor, B: Tensor, target: Tensor, store_probs: bool) -> tuple[Optional[Tensor], Tensor, Tensor, Tensor]:
@@ -381,8 +388,8 @@ def qknorm_rope_bwd(
     nv = dv.shape[1] if dv is not None else 0
     grad = torch.empty(M, size_qk + nv, dtype=x.dtype, device=x.device)
     dgamma = torch.empty(2 * head_dim, dtype=torch.float32, device=x.device)
-    nbytes = int(lib.coda_b200_qknorm_rope_bwd_scratch_bytes(M, head_dim))
-    scratch = torch.empty(nbytes // 4, dtype=torch.float32, device=x.device)
+    blocks = (M + _QK_BWD_ROWS_PER_BLOCK - 1) // _QK_BWD_ROWS_PER_BLOCK  # = coda_b200_qknorm_rope_bwd_scratch_bytes / (8 * head_dim)
+    scratch = torch.empty(blocks * 2 * head_dim, dtype=torch.float32, device=x.device)
     _qknorm_rope_bwd_out(
         dq, dk, dv, x, head_mean_sq, gamma.contiguous(), pos.contiguous(), freq.contiguous(), head_dim, num_heads_q,
         num_heads_k, float(eps), grad, dgamma, scratch,
