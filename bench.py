@@ -201,13 +201,14 @@ class Workload:
         self.h2d_bytes = sum(v.numel() * v.element_size() for v in host.values())
         self.host_out: dict[str, torch.Tensor] = {}
 
-    def upload(self):
+    def upload(self, dst: dict | None = None):
+        dst = self.dev if dst is None else dst
         for k, v in self.host.items():
-            self.dev[k].copy_(v, non_blocking=True)
+            dst[k].copy_(v, non_blocking=True)
 
-    def step(self):
+    def step(self, dev_inputs: dict | None = None):
         """Forward + backward through the public operator API.  Returns the result tensors."""
-        ck, d = self.ck, self.dev
+        ck, d = self.ck, (self.dev if dev_inputs is None else dev_inputs)
         x = d["x"].detach().requires_grad_(True)
         w = d["weight"].detach().requires_grad_(True)
         if self.op == "swiglu":
@@ -404,18 +405,49 @@ def main() -> None:
     flops = algorithmic_flops(args.op, wl.shape)
     value = flops / (ms_step * 1e-3) / 1e12
 
-    # ---- end to end: host buffers in, host buffers out, every step
+    # ---- end to end: host buffers in, host buffers out, every step.  The copies of step i+1 / i-1 run on their
+    # own streams while step i computes (double-buffered inputs), as an input pipeline would.
     e2e = None
     if not args.no_e2e:
-        d2h = 0
-        for _ in range(2):
-            wl.upload()
-            d2h = wl.download(full_step())
+        compute = torch.cuda.current_stream()
+        up, down = torch.cuda.Stream(), torch.cuda.Stream()
+        bufs = [wl.dev, {k: torch.empty_like(v) for k, v in wl.dev.items()}]
+        ev_up = [torch.cuda.Event(), torch.cuda.Event()]
+        ev_free = [torch.cuda.Event(), torch.cuda.Event()]
+        ev_done = torch.cuda.Event()
+
+        def e2e_loop(n):
+            nbytes = 0
+            with torch.cuda.stream(up):
+                wl.upload(bufs[0])
+                ev_up[0].record(up)
+            for i in range(n):
+                b = i % 2
+                if i + 1 < n:
+                    with torch.cuda.stream(up):
+                        if i >= 1:
+                            up.wait_event(ev_free[1 - b])
+                        wl.upload(bufs[1 - b])
+                        ev_up[1 - b].record(up)
+                compute.wait_event(ev_up[b])
+                res = wl.step(bufs[b])
+                if args.reduce_dx and world > 1:
+                    parallel.allreduce_partial_dx(res["dx"])
+                ev_free[b].record(compute)
+                ev_done.record(compute)
+                with torch.cuda.stream(down):
+                    down.wait_event(ev_done)
+                    nbytes = wl.download(res)
+                    for t_ in res.values():
+                        t_.record_stream(down)
+            compute.wait_stream(down)
+            compute.wait_stream(up)
+            return nbytes
+
+        d2h = e2e_loop(3)
         barrier()
         e0.record()
-        for _ in range(args.steps):
-            wl.upload()
-            d2h = wl.download(full_step())
+        d2h = e2e_loop(args.steps)
         e1.record()
         barrier()
         t = torch.tensor([e0.elapsed_time(e1)], device=device)

@@ -149,9 +149,10 @@ __global__ void __launch_bounds__(256) ce_grad_fixup_kernel(__nv_bfloat16* __res
 constexpr int kQkRowsPerBlock = 16;
 constexpr int kQkWarps = 8;
 
-// One warp per (row, head): un-rotate dy, take the RMSNorm VJP at the saved
-// statistic, accumulate the gamma gradient in registers; at the end the block
-// folds its warps and writes one partial row of [gamma_q | gamma_k] sums.
+// A group of kHD/8 lanes owns one (row, head): each lane handles 8 consecutive elements (16-byte accesses), so a
+// warp works on 2 (kHD = 128) or 4 (kHD = 64) heads of a row at once.  Per head: un-rotate dy, take the RMSNorm
+// VJP at the saved statistic, accumulate the gamma gradient in registers; at the end the block folds its warps
+// and writes one partial row of [gamma_q | gamma_k] sums.
 template <int kHD>
 __global__ void __launch_bounds__(kQkWarps * 32)
 qknorm_rope_bwd_kernel(const __nv_bfloat16* __restrict__ dq, long long ld_dq, const __nv_bfloat16* __restrict__ dk,
@@ -160,61 +161,72 @@ qknorm_rope_bwd_kernel(const __nv_bfloat16* __restrict__ dq, long long ld_dq, co
                        const __nv_bfloat16* __restrict__ gamma, const void* __restrict__ positions, int pos_is_float,
                        const float* __restrict__ freq, int hq, int hk, float eps, __nv_bfloat16* __restrict__ grad,
                        long long ld_grad, float* __restrict__ partials, int M) {
-  constexpr int kE = kHD / 32;  // elements per lane (4 or 2)
+  constexpr int kG = kHD / 8;     // lanes per head
+  constexpr int kHPW = 32 / kG;   // heads per warp iteration
   constexpr float kTwoPi = 6.283185307179586f;
-  __shared__ float red[kQkWarps][2 * kHD];
+  __shared__ float red[kQkWarps * kHPW][2 * kHD];
+  __shared__ float gam_s[2 * kHD];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int sub = lane % kG, grp = lane / kG;
   const int heads = hq + hk;
   const int row0 = blockIdx.x * kQkRowsPerBlock;
   const int nrows = min(kQkRowsPerBlock, M - row0);
-  const int e0 = lane * kE;
+  const int e0 = sub * 8;
+  for (int c = threadIdx.x; c < 2 * kHD; c += blockDim.x) gam_s[c] = __bfloat162float(gamma[c]);
+  __syncthreads();
 
-  float gq[kE], gk[kE], gam_q[kE], gam_k[kE];
+  float gq[8], gk[8];
 #pragma unroll
-  for (int j = 0; j < kE; ++j) {
+  for (int j = 0; j < 8; ++j) {
     gq[j] = 0.f;
     gk[j] = 0.f;
-    gam_q[j] = __bfloat162float(gamma[e0 + j]);
-    gam_k[j] = __bfloat162float(gamma[kHD + e0 + j]);
   }
 
-  const int items = nrows * heads;
+  const int groups_per_row = (heads + kHPW - 1) / kHPW;
+  const int items = nrows * groups_per_row;
+#pragma unroll 2
   for (int it = warp; it < items; it += kQkWarps) {
-    const int r_local = it / heads;
-    const int head = it - r_local * heads;
+    const int r_local = it / groups_per_row;
+    const int head = (it - r_local * groups_per_row) * kHPW + grp;
     const int row = row0 + r_local;
+    const bool active = head < heads;
     const bool is_q = head < hq;
-    const __nv_bfloat16* dy_p = is_q ? dq + row * ld_dq + head * kHD + e0 : dk + row * ld_dk + (head - hq) * kHD + e0;
-    const __nv_bfloat16* x_p = preact + row * ld_pre + head * kHD + e0;
-    const float* f_p = freq + head * kHD + e0;
-    const float pos = pos_is_float ? reinterpret_cast<const float*>(positions)[row]
-                                   : static_cast<float>(reinterpret_cast<const int*>(positions)[row]);
-    float dy[kE], xh[kE], fr[kE];
-    if constexpr (kE == 4) {
-      const uint2 a = *reinterpret_cast<const uint2*>(dy_p);
-      const uint2 b = *reinterpret_cast<const uint2*>(x_p);
-      const float4 f = *reinterpret_cast<const float4*>(f_p);
-      float2 t;
-      t = unpack_bf16x2(a.x); dy[0] = t.x; dy[1] = t.y;
-      t = unpack_bf16x2(a.y); dy[2] = t.x; dy[3] = t.y;
-      t = unpack_bf16x2(b.x); xh[0] = t.x; xh[1] = t.y;
-      t = unpack_bf16x2(b.y); xh[2] = t.x; xh[3] = t.y;
-      fr[0] = f.x; fr[1] = f.y; fr[2] = f.z; fr[3] = f.w;
+    float dy[8], xh[8], fr[8];
+    float pos = 0.f, r = 0.f;
+    if (active) {
+      const __nv_bfloat16* dy_p = is_q ? dq + row * ld_dq + head * kHD + e0 : dk + row * ld_dk + (head - hq) * kHD + e0;
+      const uint4 a = *reinterpret_cast<const uint4*>(dy_p);
+      const uint4 b = *reinterpret_cast<const uint4*>(preact + row * ld_pre + head * kHD + e0);
+      const float4 f0 = *reinterpret_cast<const float4*>(freq + head * kHD + e0);
+      const float4 f1 = *reinterpret_cast<const float4*>(freq + head * kHD + e0 + 4);
+      pos = pos_is_float ? reinterpret_cast<const float*>(positions)[row]
+                         : static_cast<float>(reinterpret_cast<const int*>(positions)[row]);
+      r = rsqrtf(mean_sq[static_cast<long long>(row) * heads + head] + eps);
+      const uint32_t aw[4] = {a.x, a.y, a.z, a.w}, bw[4] = {b.x, b.y, b.z, b.w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        float2 t = unpack_bf16x2(aw[j]);
+        dy[2 * j] = t.x;
+        dy[2 * j + 1] = t.y;
+        t = unpack_bf16x2(bw[j]);
+        xh[2 * j] = t.x;
+        xh[2 * j + 1] = t.y;
+      }
+      fr[0] = f0.x; fr[1] = f0.y; fr[2] = f0.z; fr[3] = f0.w;
+      fr[4] = f1.x; fr[5] = f1.y; fr[6] = f1.z; fr[7] = f1.w;
     } else {
-      const uint32_t a = *reinterpret_cast<const uint32_t*>(dy_p);
-      const uint32_t b = *reinterpret_cast<const uint32_t*>(x_p);
-      const float2 f = *reinterpret_cast<const float2*>(f_p);
-      float2 t;
-      t = unpack_bf16x2(a); dy[0] = t.x; dy[1] = t.y;
-      t = unpack_bf16x2(b); xh[0] = t.x; xh[1] = t.y;
-      fr[0] = f.x; fr[1] = f.y;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        dy[j] = 0.f;
+        xh[j] = 0.f;
+        fr[j] = 0.f;
+      }
     }
-    const float ms = mean_sq[static_cast<long long>(row) * heads + head];
-    const float r = rsqrtf(ms + eps);
-    float dz[kE];
+    const float* gam = gam_s + (is_q ? 0 : kHD) + e0;
+    float dz[8];
     float dot = 0.f;
 #pragma unroll
-    for (int p = 0; p < kE / 2; ++p) {
+    for (int p = 0; p < 4; ++p) {
       const float hi = fr[2 * p], lo = fr[2 * p + 1];
       const float t = pos * hi;
       const float terr = fmaf(pos, hi, -t);
@@ -227,28 +239,24 @@ qknorm_rope_bwd_kernel(const __nv_bfloat16* __restrict__ dq, long long ld_dq, co
       dz[2 * p + 1] = b * cs - a * sn;
     }
 #pragma unroll
-    for (int j = 0; j < kE; ++j) {
-      const float g = is_q ? gam_q[j] : gam_k[j];
-      dot = fmaf(dz[j] * g, xh[j], dot);
+    for (int j = 0; j < 8; ++j) dot = fmaf(dz[j] * gam[j], xh[j], dot);
+#pragma unroll
+    for (int o = kG / 2; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
+    const float coef = dot * r * r * r * (1.0f / kHD);
+    uint32_t ow[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float o0 = r * gam[2 * j] * dz[2 * j] - xh[2 * j] * coef;
+      const float o1 = r * gam[2 * j + 1] * dz[2 * j + 1] - xh[2 * j + 1] * coef;
+      ow[j] = pack_bf16x2(o0, o1);
     }
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
-    const float coef = dot * r * r * r * (1.0f / kHD);
-    float out[kE];
-#pragma unroll
-    for (int j = 0; j < kE; ++j) {
-      const float g = is_q ? gam_q[j] : gam_k[j];
-      out[j] = r * g * dz[j] - xh[j] * coef;
-      const float dgj = dz[j] * xh[j] * r;
+    for (int j = 0; j < 8; ++j) {
+      const float dgj = dz[j] * xh[j] * r;  // zero for inactive lanes
       if (is_q) gq[j] += dgj;
       else gk[j] += dgj;
     }
-    __nv_bfloat16* o_p = grad + row * ld_grad + head * kHD + e0;
-    if constexpr (kE == 4) {
-      *reinterpret_cast<uint2*>(o_p) = make_uint2(pack_bf16x2(out[0], out[1]), pack_bf16x2(out[2], out[3]));
-    } else {
-      *reinterpret_cast<uint32_t*>(o_p) = pack_bf16x2(out[0], out[1]);
-    }
+    if (active) *reinterpret_cast<uint4*>(grad + row * ld_grad + head * kHD + e0) = make_uint4(ow[0], ow[1], ow[2], ow[3]);
   }
 
   // copy dv next to grad_pre so that one GEMM consumes [grad_pre | dv]
@@ -265,15 +273,15 @@ qknorm_rope_bwd_kernel(const __nv_bfloat16* __restrict__ dq, long long ld_dq, co
   }
 
 #pragma unroll
-  for (int j = 0; j < kE; ++j) {
-    red[warp][e0 + j] = gq[j];
-    red[warp][kHD + e0 + j] = gk[j];
+  for (int j = 0; j < 8; ++j) {
+    red[warp * kHPW + grp][e0 + j] = gq[j];
+    red[warp * kHPW + grp][kHD + e0 + j] = gk[j];
   }
   __syncthreads();
   for (int c = threadIdx.x; c < 2 * kHD; c += blockDim.x) {
     float s = 0.f;
 #pragma unroll
-    for (int w = 0; w < kQkWarps; ++w) s += red[w][c];
+    for (int w = 0; w < kQkWarps * kHPW; ++w) s += red[w][c];
     partials[static_cast<long long>(blockIdx.x) * (2 * kHD) + c] = s;
   }
 }
@@ -384,10 +392,9 @@ extern "C" int coda_b200_qknorm_rope_bwd(const void* dq, int64_t ld_dq, const vo
   if (M <= 0 || hq < 0 || hk < 0 || hq + hk <= 0) return fail(kBadArgument, "bad extents");
   if ((hq > 0 && !dq) || (hk > 0 && !dk)) return fail(kBadArgument, "dq / dk required");
   if (scratch_bytes < coda_b200_qknorm_rope_bwd_scratch_bytes(M, head_dim)) return fail(kBadArgument, "scratch buffer too small");
-  // 8-byte vector accesses on dq / dk / preact / grad rows, 16-byte on dv and frequencies
-  if (ld_dq % 4 || ld_dk % 4 || ld_pre % 4 || ld_grad % 8) return fail(kBadArgument, "row strides must be multiples of 4 (grad: 8) elements");
-  if ((reinterpret_cast<uintptr_t>(dq) & 7u) || (reinterpret_cast<uintptr_t>(dk) & 7u) || (reinterpret_cast<uintptr_t>(preact) & 7u) ||
-      !aligned16(grad) || !aligned16(frequencies))
+  // 16-byte vector accesses on every row
+  if (ld_dq % 8 || ld_dk % 8 || ld_pre % 8 || ld_grad % 8) return fail(kBadArgument, "row strides must be multiples of 8 elements");
+  if ((hq > 0 && !aligned16(dq)) || (hk > 0 && !aligned16(dk)) || !aligned16(preact) || !aligned16(grad) || !aligned16(frequencies))
     return fail(kBadArgument, "misaligned pointer");
   if (dv != nullptr && (nv <= 0 || nv % 8 || ld_dv % 8 || !aligned16(dv))) return fail(kBadArgument, "bad dv extent / alignment");
   const int blocks = (M + kQkRowsPerBlock - 1) / kQkRowsPerBlock;
