@@ -345,6 +345,7 @@ def main() -> None:
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-clocks", action="store_true", help="do not sample nvidia-smi during the timed region")
+    ap.add_argument("--no-graph", action="store_true", help="launch every step from Python instead of replaying a CUDA graph of one step")
     ap.add_argument("--reduce-dx", action="store_true", help="all-reduce the partial dx over ranks inside the step")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
@@ -387,11 +388,33 @@ def main() -> None:
     for _ in range(args.warmup):
         full_step()
     barrier()
+    # One step (forward, backward, collectives) captured once and replayed: the same public-API calls, minus the
+    # per-launch host work, which matters once a step is only a millisecond or two of GPU time.
+    graph = None
+    if not args.no_graph:
+        try:
+            side = torch.cuda.Stream()
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                full_step()
+            torch.cuda.current_stream().wait_stream(side)
+            torch.cuda.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, capture_error_mode="thread_local"):
+                graph_res = full_step()
+            graph.replay()
+            torch.cuda.synchronize()
+        except Exception as ex:  # noqa: BLE001
+            print(f"[bench] CUDA graph capture failed ({type(ex).__name__}: {ex}); timing eager launches", file=sys.stderr)
+            graph = None
+            torch.cuda.synchronize()
+    run_step = graph.replay if graph is not None else full_step
+    barrier()
     mark0 = sampler.mark()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     for _ in range(args.steps):
-        res = full_step()
+        run_step()
     e1.record()
     barrier()
     mark1 = sampler.mark()
@@ -493,7 +516,7 @@ def main() -> None:
             "data": "synthetic",
             "config": {"workload": workload_name(args.op) + (f" [rows reduced to {args.rows}]" if args.rows else ""), **s, "global_batch_tokens": s["M"],
                        "parallelism": {"swiglu": "column", "sigmoid": "column", "cross_entropy": "vocab", "qknorm_rope": "head"}[args.op] + f"-parallel x{world}",
-                       "dx_allreduce": bool(args.reduce_dx and world > 1),
+                       "dx_allreduce": bool(args.reduce_dx and world > 1), "cuda_graph": graph is not None,
                        "l2": f"no flush: each step streams {wl.h2d_bytes / 1e6:.0f} MB of inputs plus larger intermediates, above the 126 MB L2"},
             "tokens_per_s": s["M"] / (ms_step * 1e-3),
             "frac_of_peak": value / (world * peak),
