@@ -524,8 +524,17 @@ def main() -> None:
             "clocks": clocks, "e2e": e2e, "gpu_launches": wl.kernels_per_step * args.steps, "roofline": roofline, "cpu_baseline": cpu,
         }
         print(json.dumps(line), flush=True)
+    # Leave without tearing NCCL down: destroying a communicator whose collectives were captured in a CUDA graph
+    # blocked ranks forever on this stack, after the result line had been printed.  Everything is synchronised
+    # and flushed first, then every rank exits at once.
+    graph = None
+    torch.cuda.synchronize()
     if world > 1:
-        torch.distributed.destroy_process_group()
+        torch.distributed.barrier()
+        torch.cuda.synchronize()
+    sys.stdout.flush()
+    sys.stderr.flush()
+    os._exit(0)
 
 
 if __name__ == "__main__":
