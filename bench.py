@@ -320,7 +320,7 @@ def run_reference_arm(args, rank: int) -> None:
         "e2e": {"value": tflops, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
-    print(json.dumps(line), flush=True)
+    emit_result(line)
 
 
 def workload_name(op: str) -> str:
@@ -333,7 +333,29 @@ def workload_name(op: str) -> str:
 
 
 # ------------------------------------------------------------------------------------------------ main
+_RESULT_FD = None
+
+
+def _claim_stdout() -> None:
+    """Point fd 1 at stderr for the rest of the process and keep the real stdout for the one result line:
+    libraries (NCCL's version banner, for one) write to fd 1 behind Python's back."""
+    global _RESULT_FD
+    sys.stdout.flush()
+    _RESULT_FD = os.dup(1)
+    os.dup2(2, 1)
+
+
+def emit_result(line: dict) -> None:
+    data = (json.dumps(line) + "\n").encode()
+    if _RESULT_FD is None:
+        sys.stdout.write(data.decode())
+        sys.stdout.flush()
+    else:
+        os.write(_RESULT_FD, data)
+
+
 def main() -> None:
+    _claim_stdout()
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=50)
@@ -523,7 +545,7 @@ def main() -> None:
             "frac_of_sustained_peak": value / (world * float(peaks.get("bf16_tflops_sustained", FALLBACK_PEAKS["bf16_tflops_sustained"]))),
             "clocks": clocks, "e2e": e2e, "gpu_launches": wl.kernels_per_step * args.steps, "roofline": roofline, "cpu_baseline": cpu,
         }
-        print(json.dumps(line), flush=True)
+        emit_result(line)
     # Leave without tearing NCCL down: destroying a communicator whose collectives were captured in a CUDA graph
     # blocked ranks forever on this stack, after the result line had been printed.  Everything is synchronised
     # and flushed first, then every rank exits at once.
