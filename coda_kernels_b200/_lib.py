@@ -36,6 +36,12 @@ SIGNATURES = {
         _I,
         [_P, _L, _L, _P, _L, _L, _P, _L, _P, _L, _P, _L, _P, _P, _P, _I, _P, _I, _I, _I, _F, _I, _I, _I, _P, _P],
     ),
+    "coda_b200_gemm_rmsnorm_swiglu": (_I, [_P, _L, _L, _P, _L, _L, _P, _P, _L, _P, _L, _I, _I, _I, _P, _P]),
+    "coda_b200_gemm_rmsnorm_lse": (_I, [_P, _L, _L, _P, _L, _L, _P, _P, _L, _P, _P, _P, _P, _I, _I, _I, _P, _P]),
+    "coda_b200_gemm_rmsnorm_qknorm_rope": (
+        _I,
+        [_P, _L, _L, _P, _L, _L, _P, _P, _L, _P, _L, _P, _L, _P, _P, _P, _I, _P, _I, _I, _I, _F, _I, _I, _I, _P, _P],
+    ),
     "coda_b200_dswiglu": (_I, [_P, _L, _P, _L, _P, _L, _I, _I, _P]),
     "coda_b200_dsigmoid": (_I, [_P, _L, _I, _P, _L, _P, _L, _I, _I, _P]),
     "coda_b200_qknorm_rope_bwd_scratch_bytes": (_L, [_I, _I]),

@@ -84,12 +84,14 @@ struct EpiSwiGLU {
     long long ld_pre;
     __nv_bfloat16* postact;  // [M, N/2]
     long long ld_post;
+    const float* row_scale;  // [M] fp32 or nullptr: acc is multiplied by row_scale[row] first (deferred RMSNorm)
   };
   __device__ static void prologue(const Params&, uint8_t*, int) {}
 
   template <int kBN>
   __device__ static void run(const Params& p, const EpiCtx& c, uint8_t*) {
     const bool row_ok = c.row < c.M;
+    const float rs = (p.row_scale != nullptr && row_ok) ? __ldg(p.row_scale + c.row) : 1.0f;
     __nv_bfloat16* pre = p.preact + static_cast<long long>(c.row) * p.ld_pre + c.n0;
     __nv_bfloat16* post = p.postact + static_cast<long long>(c.row) * p.ld_post + c.n0 / 2;
 #pragma unroll 1
@@ -102,7 +104,9 @@ struct EpiSwiGLU {
       float o[16];
 #pragma unroll
       for (int j = 0; j < 16; ++j) {
-        const float g = v[2 * j], u = v[2 * j + 1];
+        const float g = v[2 * j] * rs, u = v[2 * j + 1] * rs;
+        v[2 * j] = g;
+        v[2 * j + 1] = u;
         o[j] = g * fast_sigmoid(g) * u;
       }
       if (row_ok) {
@@ -141,6 +145,7 @@ struct EpiLse {
     int tiles_n;
     const int* target;    // [M]
     float* target_logit;  // [M]; written only by the tile holding the target column
+    const float* row_scale;  // [M] fp32 or nullptr: logits = acc * row_scale[row] (deferred RMSNorm)
   };
   __device__ static void prologue(const Params&, uint8_t*, int) {}
 
@@ -149,6 +154,7 @@ struct EpiLse {
     const bool row_ok = c.row < c.M;
     const int nvalid = min(kBN, c.N - c.n0);  // valid columns in this tile (>= 1)
     constexpr float kLog2e = 1.4426950408889634f;
+    const float rs = (p.row_scale != nullptr && row_ok) ? __ldg(p.row_scale + c.row) : 1.0f;
     // pass 1: row maximum over the tile
     float mx = -INFINITY;
 #pragma unroll 1
@@ -160,7 +166,7 @@ struct EpiLse {
       const int lim = nvalid - ch * 32;
 #pragma unroll
       for (int j = 0; j < 32; ++j)
-        if (j < lim) mx = fmaxf(mx, v[j]);
+        if (j < lim) mx = fmaxf(mx, v[j] * rs);
     }
     // pass 2: exponentials, their sum, target logit, optional store
     const int tgt = row_ok ? __ldg(p.target + c.row) : -1;
@@ -179,11 +185,12 @@ struct EpiLse {
       if (trel >= 0 && trel < 32) {
 #pragma unroll
         for (int j = 0; j < 32; ++j)
-          if (j == trel) tlogit = v[j];
+          if (j == trel) tlogit = v[j] * rs;
       }
+      const float rsl = rs * kLog2e;
 #pragma unroll
       for (int j = 0; j < 32; ++j) {
-        const float e = (j < lim) ? fast_exp2(fmaf(v[j], kLog2e, -mxs)) : 0.f;
+        const float e = (j < lim) ? fast_exp2(fmaf(v[j], rsl, -mxs)) : 0.f;
         sum += e;
         v[j] = e;
       }
@@ -223,6 +230,7 @@ struct EpiQKNormRope {
     const float* freq;  // [(hq + hk) * kHD] interleaved (hi, lo)
     int hq, hk;
     float eps;
+    const float* row_scale;  // [M] fp32 or nullptr: q, k (statistic and output) and v use acc * row_scale[row]; preact keeps acc
   };
   __device__ static void prologue(const Params&, uint8_t*, int) {}
 
@@ -234,6 +242,7 @@ struct EpiQKNormRope {
                                      : static_cast<float>(__ldg(reinterpret_cast<const int*>(p.positions) + safe_row));
     const int nheads_qk = p.hq + p.hk;
     constexpr float kTwoPi = 6.283185307179586f;
+    const float rs = (p.row_scale != nullptr && row_ok) ? __ldg(p.row_scale + c.row) : 1.0f;
 #pragma unroll 1
     for (int h = 0; h < kBN / kHD; ++h) {
       const int col0 = c.n0 + h * kHD;
@@ -248,6 +257,8 @@ struct EpiQKNormRope {
           float v[32];
           tmem_ld32(t0 + ch * 32, v);
           tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] *= rs;
           if (row_ok) store_row32(vrow + ch * 32, v, 32);
         }
         continue;
@@ -262,8 +273,8 @@ struct EpiQKNormRope {
 #pragma unroll
         for (int j = 0; j < 32; ++j) ss = fmaf(v[j], v[j], ss);
       }
-      const float ms = ss * (1.0f / kHD);
-      const float r = rsqrtf(ms + p.eps);
+      const float ms = ss * (1.0f / kHD) * rs * rs;  // statistic of acc * row_scale
+      const float r = rsqrtf(ms + p.eps) * rs;
       if (row_ok) p.mean_sq[static_cast<long long>(c.row) * nheads_qk + head] = ms;
       const __nv_bfloat16* gam = p.gamma + (head < p.hq ? 0 : kHD);
       __nv_bfloat16* prow = p.preact + static_cast<long long>(c.row) * p.ld_pre + col0;

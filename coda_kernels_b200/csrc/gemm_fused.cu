@@ -11,9 +11,10 @@ constexpr int kTileN = 256;  // column-tile width of every fused GEMM in this fi
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 }  // namespace
 
-extern "C" int coda_b200_gemm_swiglu(const void* A, int64_t a_stride_m, int64_t a_stride_k, const void* B,
-                                     int64_t b_stride_k, int64_t b_stride_n, void* preact, int64_t ld_pre, void* postact,
-                                     int64_t ld_post, int M, int N, int K, int* dev_status, void* stream) {
+extern "C" int coda_b200_gemm_rmsnorm_swiglu(const void* A, int64_t a_stride_m, int64_t a_stride_k, const void* B,
+                                             int64_t b_stride_k, int64_t b_stride_n, const float* rstd, void* preact,
+                                             int64_t ld_pre, void* postact, int64_t ld_post, int M, int N, int K,
+                                             int* dev_status, void* stream) {
   if (!A || !B || !preact || !postact) return fail(kBadArgument, "NULL matrix pointer");
   if (N % 16 != 0) return fail(kBadArgument, "SwiGLU needs N (= 2F) to be a multiple of 16");
   if (ld_pre % 8 != 0 || ld_post % 8 != 0 || ld_pre < N || ld_post < N / 2)
@@ -24,17 +25,25 @@ extern "C" int coda_b200_gemm_swiglu(const void* A, int64_t a_stride_m, int64_t 
   ep.ld_pre = ld_pre;
   ep.postact = static_cast<__nv_bfloat16*>(postact);
   ep.ld_post = ld_post;
+  ep.row_scale = rstd;
   Operand a{A, a_stride_m, a_stride_k};
   Operand b{B, b_stride_n, b_stride_k};
   return launch_gemm<EpiSwiGLU, 0>(a, b, M, N, K, ep, dev_status, static_cast<cudaStream_t>(stream));
 }
 
+extern "C" int coda_b200_gemm_swiglu(const void* A, int64_t a_stride_m, int64_t a_stride_k, const void* B,
+                                     int64_t b_stride_k, int64_t b_stride_n, void* preact, int64_t ld_pre, void* postact,
+                                     int64_t ld_post, int M, int N, int K, int* dev_status, void* stream) {
+  return coda_b200_gemm_rmsnorm_swiglu(A, a_stride_m, a_stride_k, B, b_stride_k, b_stride_n, nullptr, preact, ld_pre, postact,
+                                       ld_post, M, N, K, dev_status, stream);
+}
+
 extern "C" int coda_b200_lse_tiles(int N) { return (N + kTileN - 1) / kTileN; }
 
-extern "C" int coda_b200_gemm_lse(const void* A, int64_t a_stride_m, int64_t a_stride_k, const void* B, int64_t b_stride_k,
-                                  int64_t b_stride_n, void* P, int64_t ldp, float* part_max, float* part_sum,
-                                  const int32_t* target, float* target_logit, int M, int N, int K, int* dev_status,
-                                  void* stream) {
+extern "C" int coda_b200_gemm_rmsnorm_lse(const void* A, int64_t a_stride_m, int64_t a_stride_k, const void* B,
+                                          int64_t b_stride_k, int64_t b_stride_n, const float* rstd, void* P, int64_t ldp,
+                                          float* part_max, float* part_sum, const int32_t* target, float* target_logit, int M,
+                                          int N, int K, int* dev_status, void* stream) {
   if (!A || !B || !part_max || !part_sum || !target || !target_logit) return fail(kBadArgument, "NULL pointer");
   if (N % 8 != 0) return fail(kBadArgument, "N must be a multiple of 8");
   Operand a{A, a_stride_m, a_stride_k};
@@ -50,6 +59,7 @@ extern "C" int coda_b200_gemm_lse(const void* A, int64_t a_stride_m, int64_t a_s
     ep.tiles_n = tiles_n;
     ep.target = target;
     ep.target_logit = target_logit;
+    ep.row_scale = rstd;
     return launch_gemm<EpiLse<true>, 0>(a, b, M, N, K, ep, dev_status, static_cast<cudaStream_t>(stream));
   }
   EpiLse<false>::Params ep;
@@ -60,14 +70,23 @@ extern "C" int coda_b200_gemm_lse(const void* A, int64_t a_stride_m, int64_t a_s
   ep.tiles_n = tiles_n;
   ep.target = target;
   ep.target_logit = target_logit;
+  ep.row_scale = rstd;
   return launch_gemm<EpiLse<false>, 0>(a, b, M, N, K, ep, dev_status, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int coda_b200_gemm_lse(const void* A, int64_t a_stride_m, int64_t a_stride_k, const void* B, int64_t b_stride_k,
+                                  int64_t b_stride_n, void* P, int64_t ldp, float* part_max, float* part_sum,
+                                  const int32_t* target, float* target_logit, int M, int N, int K, int* dev_status,
+                                  void* stream) {
+  return coda_b200_gemm_rmsnorm_lse(A, a_stride_m, a_stride_k, B, b_stride_k, b_stride_n, nullptr, P, ldp, part_max, part_sum,
+                                    target, target_logit, M, N, K, dev_status, stream);
 }
 
 namespace {
 template <int kHD>
 int run_qknorm(const Operand& a, const Operand& b, void* qk, int64_t ld_qk, void* preact, int64_t ld_pre, void* v, int64_t ld_v,
                float* mean_sq, const void* gamma, const void* positions, int pos_is_float, const float* frequencies, int hq,
-               int hk, float eps, int M, int N, int K, int* dev_status, void* stream) {
+               int hk, float eps, const float* rstd, int M, int N, int K, int* dev_status, void* stream) {
   typename EpiQKNormRope<kHD>::Params ep;
   ep.qk = static_cast<__nv_bfloat16*>(qk);
   ep.ld_qk = ld_qk;
@@ -83,15 +102,17 @@ int run_qknorm(const Operand& a, const Operand& b, void* qk, int64_t ld_qk, void
   ep.hq = hq;
   ep.hk = hk;
   ep.eps = eps;
+  ep.row_scale = rstd;
   return launch_gemm<EpiQKNormRope<kHD>, 0>(a, b, M, N, K, ep, dev_status, static_cast<cudaStream_t>(stream));
 }
 }  // namespace
 
-extern "C" int coda_b200_gemm_qknorm_rope(const void* A, int64_t a_stride_m, int64_t a_stride_k, const void* B,
-                                          int64_t b_stride_k, int64_t b_stride_n, void* qk, int64_t ld_qk, void* preact,
-                                          int64_t ld_pre, void* v, int64_t ld_v, float* mean_sq, const void* gamma,
-                                          const void* positions, int pos_is_float, const float* frequencies, int head_dim,
-                                          int hq, int hk, float eps, int M, int N, int K, int* dev_status, void* stream) {
+extern "C" int coda_b200_gemm_rmsnorm_qknorm_rope(const void* A, int64_t a_stride_m, int64_t a_stride_k, const void* B,
+                                                  int64_t b_stride_k, int64_t b_stride_n, const float* rstd, void* qk,
+                                                  int64_t ld_qk, void* preact, int64_t ld_pre, void* v, int64_t ld_v,
+                                                  float* mean_sq, const void* gamma, const void* positions, int pos_is_float,
+                                                  const float* frequencies, int head_dim, int hq, int hk, float eps, int M,
+                                                  int N, int K, int* dev_status, void* stream) {
   if (!A || !B || !qk || !preact || !mean_sq || !gamma || !positions || !frequencies)
     return fail(kBadArgument, "NULL pointer");
   if (head_dim != 64 && head_dim != 128) return fail(kBadArgument, "head_dim must be 64 or 128");
@@ -108,7 +129,17 @@ extern "C" int coda_b200_gemm_qknorm_rope(const void* A, int64_t a_stride_m, int
   Operand b{B, b_stride_n, b_stride_k};
   if (head_dim == 128)
     return run_qknorm<128>(a, b, qk, ld_qk, preact, ld_pre, v, ld_v, mean_sq, gamma, positions, pos_is_float, frequencies, hq,
-                           hk, eps, M, N, K, dev_status, stream);
+                           hk, eps, rstd, M, N, K, dev_status, stream);
   return run_qknorm<64>(a, b, qk, ld_qk, preact, ld_pre, v, ld_v, mean_sq, gamma, positions, pos_is_float, frequencies, hq, hk,
-                        eps, M, N, K, dev_status, stream);
+                        eps, rstd, M, N, K, dev_status, stream);
+}
+
+extern "C" int coda_b200_gemm_qknorm_rope(const void* A, int64_t a_stride_m, int64_t a_stride_k, const void* B,
+                                          int64_t b_stride_k, int64_t b_stride_n, void* qk, int64_t ld_qk, void* preact,
+                                          int64_t ld_pre, void* v, int64_t ld_v, float* mean_sq, const void* gamma,
+                                          const void* positions, int pos_is_float, const float* frequencies, int head_dim,
+                                          int hq, int hk, float eps, int M, int N, int K, int* dev_status, void* stream) {
+  return coda_b200_gemm_rmsnorm_qknorm_rope(A, a_stride_m, a_stride_k, B, b_stride_k, b_stride_n, nullptr, qk, ld_qk, preact,
+                                            ld_pre, v, ld_v, mean_sq, gamma, positions, pos_is_float, frequencies, head_dim, hq,
+                                            hk, eps, M, N, K, dev_status, stream);
 }

@@ -122,6 +122,28 @@ int coda_b200_dswiglu(const void* preact, int64_t ld_pre, const void* dout, int6
 int coda_b200_dsigmoid(const void* out, int64_t ld_out, int out_is_fp32, const void* dout, int64_t ld_dout, void* grad_pre,
                        int64_t ld_grad, int M, int N, void* stream);
 
+/* Deferred-RMSNorm variants: the same three fused GEMMs with the accumulator
+ * multiplied by a per-row fp32 scale `rstd[M]` before the epilogue math, i.e.
+ * the result of feeding rmsnorm(x) (without its weight) instead of x.
+ *   swiglu:      preact = bf16(acc * rstd), postact from the scaled pairs
+ *   lse:         logits = acc * rstd everywhere (partials, probabilities, target logit)
+ *   qknorm_rope: q, k (statistic and output) and v use acc * rstd; preact keeps
+ *                the unscaled acc, mean_sq is that of the scaled head
+ * Replace `coda::_gemm_rmsnorm_swiglu_epi`, `coda::_gemm_rmsnorm_lse_epi` and the
+ * `rstd_qknorm_rope_epi` program (coda/core/gemm/functional.py:283-334, 392-450;
+ * coda/core/gemm/epilogues.py:50-58, 262-303).  rstd == NULL gives the plain ops. */
+int coda_b200_gemm_rmsnorm_swiglu(const void* A, int64_t a_stride_m, int64_t a_stride_k, const void* B, int64_t b_stride_k,
+                                  int64_t b_stride_n, const float* rstd, void* preact, int64_t ld_pre, void* postact,
+                                  int64_t ld_post, int M, int N, int K, int* dev_status, void* stream);
+int coda_b200_gemm_rmsnorm_lse(const void* A, int64_t a_stride_m, int64_t a_stride_k, const void* B, int64_t b_stride_k,
+                               int64_t b_stride_n, const float* rstd, void* P, int64_t ldp, float* part_max, float* part_sum,
+                               const int32_t* target, float* target_logit, int M, int N, int K, int* dev_status, void* stream);
+int coda_b200_gemm_rmsnorm_qknorm_rope(const void* A, int64_t a_stride_m, int64_t a_stride_k, const void* B,
+                                       int64_t b_stride_k, int64_t b_stride_n, const float* rstd, void* qk, int64_t ld_qk,
+                                       void* preact, int64_t ld_pre, void* v, int64_t ld_v, float* mean_sq, const void* gamma,
+                                       const void* positions, int pos_is_float, const float* frequencies, int head_dim, int hq,
+                                       int hk, float eps, int M, int N, int K, int* dev_status, void* stream);
+
 /* Size in bytes of the scratch buffer coda_b200_qknorm_rope_bwd needs. */
 int64_t coda_b200_qknorm_rope_bwd_scratch_bytes(int M, int head_dim);
 

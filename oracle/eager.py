@@ -154,6 +154,36 @@ def linear_qknorm_rope(
     return rotated[:, :size_q], rotated[:, size_q:], v
 
 
+# ---------------------------------------------------------------------------------------------- deferred-RMSNorm variants
+def rmsnorm_rstd(x: torch.Tensor, eps: float, compute_dtype: torch.dtype = torch.float32) -> torch.Tensor:
+    """Each row's ``1 / sqrt(mean(x^2) + eps)`` (torch_ops.py:68-76)."""
+    return torch.rsqrt(_c(x, compute_dtype).square().mean(dim=-1) + eps)
+
+
+def gemm_rmsnorm_swiglu(A, B, rstd, compute_dtype=torch.float32):
+    """``preact = (A @ B) * rstd``, ``postact = swiglu(preact)`` (torch_ops.py:442-464); ``B`` is ``[K, 2F]``."""
+    preact = (_c(A, compute_dtype) @ _c(B, compute_dtype)) * _c(rstd, compute_dtype)[:, None]
+    return preact, F.silu(preact[:, 0::2]) * preact[:, 1::2]
+
+
+def gemm_rmsnorm_lse(A, B, rstd, compute_dtype=torch.float32):
+    """Logits ``(A @ B) * rstd`` and each row's log-sum-exp (torch_ops.py:1061-1081)."""
+    logits = (_c(A, compute_dtype) @ _c(B, compute_dtype)) * _c(rstd, compute_dtype)[:, None]
+    return logits, torch.logsumexp(logits, dim=-1)
+
+
+def gemm_rmsnorm_qknorm_rope(A, B, rstd, weight, positions, frequencies, head_dim, num_heads_q, num_heads_k, eps,
+                             compute_dtype=torch.float32):
+    """``(rotated, preact, head_mean_sq)`` where the statistic and the output use ``z = (A @ B) * rstd`` and ``preact``
+    is saved without ``rstd`` (torch_ops.py:725-777; that code rounds ``z`` to the GEMM dtype first, this one does not)."""
+    preact = _c(A, compute_dtype) @ _c(B, compute_dtype)
+    z = preact * _c(rstd, compute_dtype)[:, None]
+    ms = head_mean_square(z, head_dim)
+    normed = qknorm(z, ms, _c(weight, compute_dtype), head_dim, num_heads_q, num_heads_k, eps)
+    cos, sin = rope_tables(positions, frequencies)
+    return rope_interleaved(normed, cos, sin), preact, ms
+
+
 # ---------------------------------------------------------------------------------------------- fwd + bwd helpers
 def fwd_bwd(fn, inputs: dict, grad_names: list[str], cotangents):
     """Run ``fn(**inputs)`` with autograd on ``grad_names`` and return ``(outputs, grads)``.

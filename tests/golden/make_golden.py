@@ -92,6 +92,27 @@ def qk_case(name, M, K, d_, hq, hk, hv, seq, seed, pos_offset, float_pos=False):
                 "dgamma_bwd": dgam})
 
 
+def rstd_case(name, M, K, Fdim, V, d_, hq, hk, seed):
+    """The deferred-RMSNorm variants of the three fused GEMMs, from the reference's eager ops (run in fp64)."""
+    g = torch.Generator().manual_seed(seed)
+    x = torch.randn(M, K, generator=g).to(torch.bfloat16)
+    rstd = torch_ops.rmsnorm_rstd(x.to(F64), 1e-5).to(torch.float32)
+    w_sw = (torch.randn(2 * Fdim, K, generator=g) / K**0.5).to(torch.bfloat16)
+    w_v = (torch.randn(V, K, generator=g) / K**0.5).to(torch.bfloat16)
+    qk = synth.qknorm_rope_inputs(M, K, d_, hq, hk, 0, seq_len=M, seed=seed + 1)
+    target = torch.randint(0, V, (M,), generator=g).to(torch.int32)
+    target[::5] = -100
+    pre, post = torch_ops.gemm_rmsnorm_swiglu(x.to(F64), w_sw.to(F64).mT, rstd.to(F64), IL)
+    logits, lses = torch_ops.gemm_rmsnorm_lse(x.to(F64), w_v.to(F64).mT, rstd.to(F64), logits_dtype=F64)
+    losses, dlogits = torch_ops.cross_entropy(logits, target.long(), -100)
+    rot, preact, ms = torch_ops.gemm_rmsnorm_qknorm_rope(
+        x.to(F64), qk["weight"].to(F64).mT, rstd.to(F64), qk["gamma"].to(F64), cos=None, sin=None, positions=qk["positions"].to(F64),
+        frequencies=qk["frequencies"].to(F64), head_dim=d_, num_heads_q=hq, num_heads_k=hk, eps=1e-6, layout=IL)
+    save(name, {"x": x, "rstd": rstd, "w_swiglu": w_sw, "w_vocab": w_v, "target": target, "qk_inputs": qk,
+                "cfg": {"head_dim": d_, "hq": hq, "hk": hk, "eps": 1e-6}, "swiglu_pre": pre, "swiglu_post": post, "lse": lses,
+                "row_losses": losses, "dlogits": dlogits, "qk_rotated": rot, "qk_preact": preact, "qk_mean_sq": ms})
+
+
 if __name__ == "__main__":
     torch.manual_seed(0)
     swiglu_case("swiglu_small", 48, 64, 40, seed=1)
@@ -102,3 +123,4 @@ if __name__ == "__main__":
     qk_case("qk_gqa_d64", 24, 64, 64, 4, 2, 2, seq=12, seed=6, pos_offset=0)
     qk_case("qk_gqa_d128_far", 20, 72, 128, 2, 1, 1, seq=10, seed=7, pos_offset=1 << 20)
     qk_case("qk_mha_d64_fpos", 16, 64, 64, 2, 2, 2, seq=16, seed=8, pos_offset=5, float_pos=True)
+    rstd_case("rstd_variants", 24, 64, 24, 264, 64, 2, 1, seed=9)

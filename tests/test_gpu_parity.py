@@ -274,3 +274,46 @@ def test_bad_arguments_raise(ck):
         ck.linear_swiglu(x, w)
     with pytest.raises(NotImplementedError):
         ck.linear_swiglu(x.half(), w.half())
+
+
+# ------------------------------------------------------------------------------------------------ deferred-RMSNorm variants
+def test_rstd_variants_golden_and_oracle(ck, golden_dir):
+    from coda_kernels_b200 import ops_rmsnorm as R
+
+    g = load(golden_dir, "rstd_variants")
+    cfg, qk = g["cfg"], g["qk_inputs"]
+    x, rstd = g["x"].to(DEV), g["rstd"].to(DEV)
+    pre, post = R.gemm_rmsnorm_swiglu(x, g["w_swiglu"].to(DEV).mT, rstd)
+    close(pre, g["swiglu_pre"], what="swiglu preact")
+    close(post, g["swiglu_post"], what="swiglu postact")
+    t = g["target"].to(DEV)
+    losses, lse, dlogits = R.gemm_rmsnorm_lse_dlogits(x, g["w_vocab"].to(DEV).mT, rstd, t, -100)
+    sel_losses, sel_lse, _ = R.gemm_rmsnorm_lse_select_logits(x, g["w_vocab"].to(DEV).mT, rstd, t, -100)
+    close(lse, g["lse"], tol=LOSS_TOL, what="lse")
+    close(sel_lse, g["lse"], tol=LOSS_TOL, what="lse (select)")
+    close(losses, g["row_losses"], tol=LOSS_TOL, what="row losses")
+    close(sel_losses, g["row_losses"], tol=LOSS_TOL, what="row losses (select)")
+    close(dlogits, g["dlogits"], what="dlogits")
+    assert (dlogits[t == -100].view(torch.int16) == 0).all()
+    w = qk["weight"].to(DEV)
+    rot, preact, ms, v = R.gemm_rmsnorm_qknorm_rope(
+        x, w.mT, rstd, qk["gamma"].to(DEV), qk["positions"].to(DEV), qk["frequencies"].to(DEV), cfg["head_dim"], cfg["hq"], cfg["hk"], cfg["eps"])
+    status_ok(ck)
+    assert v is None
+    close(rot, g["qk_rotated"], what="rotated qk")
+    close(preact, g["qk_preact"], what="preact (unscaled)")
+    close(ms, g["qk_mean_sq"], tol=1e-3, what="head mean square")
+    # a larger, ragged case with v columns against the oracle: v = (x @ Wv^T) * rstd
+    d = inputs.qknorm_rope_inputs(700, 264, 128, 4, 2, 2, seq_len=512, pos_offset=9)
+    xg = d["x"].to(DEV)
+    r2 = eager.rmsnorm_rstd(xg, 1e-5)
+    size_qk = 6 * 128
+    rot, preact, ms, v = R.gemm_rmsnorm_qknorm_rope(xg, d["weight"].to(DEV).mT, r2, d["gamma"].to(DEV), d["positions"].to(DEV),
+                                                    d["frequencies"].to(DEV), 128, 4, 2, 1e-6)
+    ro, rp, rms = eager.gemm_rmsnorm_qknorm_rope(xg, d["weight"].to(DEV)[:size_qk].mT, r2, d["gamma"].to(DEV), d["positions"].to(DEV),
+                                                 d["frequencies"].to(DEV), 128, 4, 2, 1e-6)
+    status_ok(ck)
+    close(rot, ro, what="rotated qk (large)")
+    close(preact, rp, what="preact (large)")
+    close(ms, rms, tol=1e-3, what="mean square (large)")
+    close(v, (xg.float() @ d["weight"].to(DEV)[size_qk:].float().mT) * r2[:, None], what="v (large)")

@@ -89,3 +89,25 @@ def test_qknorm_rope(golden_dir, name):
         close(grads["gamma"], g["dgamma"], tol)
     # the reference's hand-written backward agrees with autograd on dgamma
     close(g["dgamma_bwd"], g["dgamma"], 1e-10)
+
+
+def test_rstd_variants(golden_dir):
+    """Deferred-RMSNorm forms of the three fused GEMMs against the reference's eager ops."""
+    g = load(golden_dir, "rstd_variants")
+    cfg, qk = g["cfg"], g["qk_inputs"]
+    for dtype, tol in ((F64, 1e-9), (torch.float32, 5e-5)):
+        pre, post = eager.gemm_rmsnorm_swiglu(g["x"], g["w_swiglu"].mT, g["rstd"], compute_dtype=dtype)
+        close(pre, g["swiglu_pre"], tol)
+        close(post, g["swiglu_post"], tol)
+        logits, lse = eager.gemm_rmsnorm_lse(g["x"], g["w_vocab"].mT, g["rstd"], compute_dtype=dtype)
+        close(lse, g["lse"], tol)
+        losses, dlogits = eager.cross_entropy_rows(logits, g["target"], -100)
+        close(losses, g["row_losses"], tol)
+        close(dlogits, g["dlogits"], tol)
+        rot, preact, ms = eager.gemm_rmsnorm_qknorm_rope(
+            g["x"], qk["weight"].mT, g["rstd"], qk["gamma"], qk["positions"], qk["frequencies"], cfg["head_dim"], cfg["hq"], cfg["hk"],
+            cfg["eps"], compute_dtype=dtype)
+        close(rot, g["qk_rotated"], tol)
+        close(preact, g["qk_preact"], tol)
+        close(ms, g["qk_mean_sq"], tol)
+    assert torch.allclose(eager.rmsnorm_rstd(g["x"], 1e-5, F64).float(), g["rstd"])
