@@ -42,6 +42,9 @@ SIGNATURES = {
         _I,
         [_P, _L, _L, _P, _L, _L, _P, _P, _L, _P, _L, _P, _L, _P, _P, _P, _I, _P, _I, _I, _I, _F, _I, _I, _I, _P, _P],
     ),
+    "coda_b200_gemm_lse_logits": (_I, [_P, _L, _L, _P, _L, _L, _P, _P, _L, _P, _P, _I, _I, _I, _P, _P]),
+    "coda_b200_lse_reduce": (_I, [_P, _P, _I, _P, _I, _P]),
+    "coda_b200_cross_entropy_fwd_bwd": (_I, [_P, _L, _P, _P, _I, _P, _I, _I, _P]),
     "coda_b200_dswiglu": (_I, [_P, _L, _P, _L, _P, _L, _I, _I, _P]),
     "coda_b200_dsigmoid": (_I, [_P, _L, _I, _P, _L, _P, _L, _I, _I, _P]),
     "coda_b200_qknorm_rope_bwd_scratch_bytes": (_L, [_I, _I]),

@@ -112,8 +112,46 @@ __global__ void __launch_bounds__(256) lse_finalize_kernel(const float* __restri
   if (lane == 0) {
     const float l = mx + logf(s);
     lse[row] = l;
-    losses[row] = (target[row] != ignore_index) ? (l - target_logit[row]) : 0.0f;
+    if (target != nullptr) losses[row] = (target[row] != ignore_index) ? (l - target_logit[row]) : 0.0f;
   }
+}
+
+// ------------------------------------------------------------------ cross entropy from stored logits, in place
+// logits[i,j] <- exp(logits[i,j] - lse[i]) - (j == target[i]), or +0 for ignored rows; the thread that holds the
+// target column also writes losses[i] = lse[i] - logit (rows that are ignored get 0 from the thread of column 0).
+__global__ void __launch_bounds__(256) ce_fwd_bwd_kernel(__nv_bfloat16* __restrict__ logits, long long ld,
+                                                         const float* __restrict__ lse, const int* __restrict__ target,
+                                                         int ignore_index, float* __restrict__ losses, int N8) {
+  const int row = blockIdx.y;
+  const int c8 = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c8 >= N8) return;
+  const int col = c8 * 8;
+  uint4* ptr = reinterpret_cast<uint4*>(logits + row * ld + col);
+  const int tgt = target[row];
+  if (tgt == ignore_index) {
+    *ptr = make_uint4(0u, 0u, 0u, 0u);
+    if (c8 == 0) losses[row] = 0.0f;
+    return;
+  }
+  const float l = lse[row];
+  const uint4 p4 = *ptr;
+  const uint32_t w[4] = {p4.x, p4.y, p4.z, p4.w};
+  uint32_t r[4];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const float2 v = unpack_bf16x2(w[j]);
+    float d0 = __expf(v.x - l), d1 = __expf(v.y - l);
+    if (col + 2 * j == tgt) {
+      losses[row] = l - v.x;
+      d0 -= 1.0f;
+    }
+    if (col + 2 * j + 1 == tgt) {
+      losses[row] = l - v.y;
+      d1 -= 1.0f;
+    }
+    r[j] = pack_bf16x2(d0, d1);
+  }
+  *ptr = make_uint4(r[0], r[1], r[2], r[3]);
 }
 
 // ------------------------------------------------------------------ softmax-gradient fix-up, in place
@@ -359,6 +397,28 @@ extern "C" int coda_b200_lse_finalize(const float* part_max, const float* part_s
   lse_finalize_kernel<<<(M + rows_per_block - 1) / rows_per_block, rows_per_block * 32, 0, static_cast<cudaStream_t>(stream)>>>(
       part_max, part_sum, tiles_n, target, target_logit, ignore_index, lse, losses, M);
   return launch_check("lse_finalize launch");
+}
+
+extern "C" int coda_b200_lse_reduce(const float* part_max, const float* part_sum, int tiles_n, float* lse, int M, void* stream) {
+  if (!part_max || !part_sum || !lse) return fail(kBadArgument, "NULL pointer");
+  if (M <= 0 || tiles_n <= 0) return fail(kBadArgument, "M and tiles_n must be positive");
+  const int rows_per_block = 8;
+  lse_finalize_kernel<<<(M + rows_per_block - 1) / rows_per_block, rows_per_block * 32, 0, static_cast<cudaStream_t>(stream)>>>(
+      part_max, part_sum, tiles_n, nullptr, nullptr, 0, lse, nullptr, M);
+  return launch_check("lse_reduce launch");
+}
+
+extern "C" int coda_b200_cross_entropy_fwd_bwd(void* logits, int64_t ld, const float* lse, const int32_t* target,
+                                               int ignore_index, float* losses, int M, int N, void* stream) {
+  if (!logits || !lse || !target || !losses) return fail(kBadArgument, "NULL pointer");
+  if (M <= 0 || N <= 0 || N % 8 != 0 || ld % 8 != 0 || ld < N || !aligned16(logits))
+    return fail(kBadArgument, "logits must be 16-byte aligned, N and ld multiples of 8");
+  if (M > 65535) return fail(kBadArgument, "M above 65535 is not supported by this grid");
+  const int N8 = N / 8;
+  dim3 grid((N8 + 255) / 256, M, 1);
+  ce_fwd_bwd_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<__nv_bfloat16*>(logits), ld, lse, target,
+                                                                        ignore_index, losses, N8);
+  return launch_check("cross_entropy_fwd_bwd launch");
 }
 
 extern "C" int coda_b200_ce_grad_fixup(void* P, int64_t ldp, const float* part_max, int tiles_n, const float* lse,

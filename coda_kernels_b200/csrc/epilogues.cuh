@@ -131,11 +131,15 @@ struct EpiSwiGLU {
 // ------------------------------------------------------------------ log-sum-exp partials (+ optional probability store)
 // Per (row, column-tile): m = max_j acc, s = sum_j exp(acc - m).  The tile that
 // contains the row's target column also records that logit (fp32, unrounded).
-// With kStoreP the tile's unnormalised probabilities exp(acc - m) are stored in
-// bf16 so that the backward never needs the logits; a later in-place pass
-// rescales them by exp(m - lse) and subtracts the one-hot.  Replaces
-// `_gemm_lse_epi` / `_lse_select_logits_epi` (coda/core/gemm/functional.py:342-368, 453-493).
-template <bool kStoreP>
+// kStore selects what else is written: kLseStoreNone nothing; kLseStoreProbs the
+// tile's unnormalised probabilities exp(acc - m) in bf16, so that the backward
+// never needs the logits (a later in-place pass rescales them by exp(m - lse)
+// and subtracts the one-hot); kLseStoreLogits the bf16 logits themselves, the
+// reference's own dataflow.  Replaces `_gemm_lse_epi` / `_lse_select_logits_epi`
+// (coda/core/gemm/functional.py:342-368, 453-493).
+constexpr int kLseStoreNone = 0, kLseStoreProbs = 1, kLseStoreLogits = 2;
+
+template <int kStore>
 struct EpiLse {
   struct Params {
     __nv_bfloat16* P;  // [M, N] or nullptr
@@ -143,7 +147,7 @@ struct EpiLse {
     float* part_max;  // [M, tiles_n]
     float* part_sum;  // [M, tiles_n]
     int tiles_n;
-    const int* target;    // [M]
+    const int* target;    // [M] or nullptr (no target pick)
     float* target_logit;  // [M]; written only by the tile holding the target column
     const float* row_scale;  // [M] fp32 or nullptr: logits = acc * row_scale[row] (deferred RMSNorm)
   };
@@ -169,10 +173,10 @@ struct EpiLse {
         if (j < lim) mx = fmaxf(mx, v[j] * rs);
     }
     // pass 2: exponentials, their sum, target logit, optional store
-    const int tgt = row_ok ? __ldg(p.target + c.row) : -1;
+    const int tgt = (row_ok && p.target != nullptr) ? __ldg(p.target + c.row) : -1;
     const int tcol = tgt - c.n0;  // target column relative to this tile
     float sum = 0.f, tlogit = 0.f;
-    __nv_bfloat16* prow = kStoreP ? p.P + static_cast<long long>(c.row) * p.ldp + c.n0 : nullptr;
+    __nv_bfloat16* prow = (kStore != kLseStoreNone) ? p.P + static_cast<long long>(c.row) * p.ldp + c.n0 : nullptr;
     const float mxs = mx * kLog2e;
 #pragma unroll 1
     for (int ch = 0; ch < kBN / 32; ++ch) {
@@ -192,9 +196,9 @@ struct EpiLse {
       for (int j = 0; j < 32; ++j) {
         const float e = (j < lim) ? fast_exp2(fmaf(v[j], rsl, -mxs)) : 0.f;
         sum += e;
-        v[j] = e;
+        v[j] = (kStore == kLseStoreLogits) ? v[j] * rs : e;
       }
-      if (kStoreP && row_ok) store_row32(prow + ch * 32, v, lim);
+      if (kStore != kLseStoreNone && row_ok) store_row32(prow + ch * 32, v, lim);
     }
     if (row_ok) {
       p.part_max[static_cast<long long>(c.row) * p.tiles_n + c.tn] = mx;

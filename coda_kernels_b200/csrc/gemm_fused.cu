@@ -51,7 +51,7 @@ extern "C" int coda_b200_gemm_rmsnorm_lse(const void* A, int64_t a_stride_m, int
   const int tiles_n = coda_b200_lse_tiles(N);
   if (P != nullptr) {
     if (!aligned16(P) || ldp % 8 != 0 || ldp < N) return fail(kBadArgument, "P must be 16-byte aligned with ldp % 8 == 0, ldp >= N");
-    EpiLse<true>::Params ep;
+    EpiLse<kLseStoreProbs>::Params ep;
     ep.P = static_cast<__nv_bfloat16*>(P);
     ep.ldp = ldp;
     ep.part_max = part_max;
@@ -60,9 +60,9 @@ extern "C" int coda_b200_gemm_rmsnorm_lse(const void* A, int64_t a_stride_m, int
     ep.target = target;
     ep.target_logit = target_logit;
     ep.row_scale = rstd;
-    return launch_gemm<EpiLse<true>, 0>(a, b, M, N, K, ep, dev_status, static_cast<cudaStream_t>(stream));
+    return launch_gemm<EpiLse<kLseStoreProbs>, 0>(a, b, M, N, K, ep, dev_status, static_cast<cudaStream_t>(stream));
   }
-  EpiLse<false>::Params ep;
+  EpiLse<kLseStoreNone>::Params ep;
   ep.P = nullptr;
   ep.ldp = 0;
   ep.part_max = part_max;
@@ -71,7 +71,7 @@ extern "C" int coda_b200_gemm_rmsnorm_lse(const void* A, int64_t a_stride_m, int
   ep.target = target;
   ep.target_logit = target_logit;
   ep.row_scale = rstd;
-  return launch_gemm<EpiLse<false>, 0>(a, b, M, N, K, ep, dev_status, static_cast<cudaStream_t>(stream));
+  return launch_gemm<EpiLse<kLseStoreNone>, 0>(a, b, M, N, K, ep, dev_status, static_cast<cudaStream_t>(stream));
 }
 
 extern "C" int coda_b200_gemm_lse(const void* A, int64_t a_stride_m, int64_t a_stride_k, const void* B, int64_t b_stride_k,
@@ -80,6 +80,27 @@ extern "C" int coda_b200_gemm_lse(const void* A, int64_t a_stride_m, int64_t a_s
                                   void* stream) {
   return coda_b200_gemm_rmsnorm_lse(A, a_stride_m, a_stride_k, B, b_stride_k, b_stride_n, nullptr, P, ldp, part_max, part_sum,
                                     target, target_logit, M, N, K, dev_status, stream);
+}
+
+extern "C" int coda_b200_gemm_lse_logits(const void* A, int64_t a_stride_m, int64_t a_stride_k, const void* B,
+                                         int64_t b_stride_k, int64_t b_stride_n, const float* rstd, void* logits, int64_t ld_logits,
+                                         float* part_max, float* part_sum, int M, int N, int K, int* dev_status, void* stream) {
+  if (!A || !B || !logits || !part_max || !part_sum) return fail(kBadArgument, "NULL pointer");
+  if (N % 8 != 0) return fail(kBadArgument, "N must be a multiple of 8");
+  if (!aligned16(logits) || ld_logits % 8 != 0 || ld_logits < N)
+    return fail(kBadArgument, "logits must be 16-byte aligned with ld % 8 == 0, ld >= N");
+  EpiLse<kLseStoreLogits>::Params ep;
+  ep.P = static_cast<__nv_bfloat16*>(logits);
+  ep.ldp = ld_logits;
+  ep.part_max = part_max;
+  ep.part_sum = part_sum;
+  ep.tiles_n = coda_b200_lse_tiles(N);
+  ep.target = nullptr;
+  ep.target_logit = nullptr;
+  ep.row_scale = rstd;
+  Operand a{A, a_stride_m, a_stride_k};
+  Operand b{B, b_stride_n, b_stride_k};
+  return launch_gemm<EpiLse<kLseStoreLogits>, 0>(a, b, M, N, K, ep, dev_status, static_cast<cudaStream_t>(stream));
 }
 
 namespace {

@@ -144,6 +144,22 @@ int coda_b200_gemm_rmsnorm_qknorm_rope(const void* A, int64_t a_stride_m, int64_
                                        const void* positions, int pos_is_float, const float* frequencies, int head_dim, int hq,
                                        int hk, float eps, int M, int N, int K, int* dev_status, void* stream);
 
+/* The reference's own cross-entropy dataflow, for callers that want the logits:
+ * coda_b200_gemm_lse_logits stores logits = bf16(acc * rstd) (rstd may be NULL)
+ * plus the LSE partials; coda_b200_lse_reduce folds the partials into lse[M];
+ * coda_b200_cross_entropy_fwd_bwd then overwrites the logits in place with
+ * exp(logit - lse) - onehot (+0 for ignored rows) and writes losses[M] = lse -
+ * logit[target] (0 if ignored; targets outside [0, N) leave losses untouched).
+ * Replace `coda::_gemm_lse_epi` + `logsumexp(partials)` and
+ * `cross_entropy_fwd_bwd` (coda/core/gemm/functional.py:337-389;
+ * coda/core/elementwise/functional.py:221-311, kernel coda/core/elementwise/cross_entropy.py:18-131). */
+int coda_b200_gemm_lse_logits(const void* A, int64_t a_stride_m, int64_t a_stride_k, const void* B, int64_t b_stride_k,
+                              int64_t b_stride_n, const float* rstd, void* logits, int64_t ld_logits, float* part_max,
+                              float* part_sum, int M, int N, int K, int* dev_status, void* stream);
+int coda_b200_lse_reduce(const float* part_max, const float* part_sum, int tiles_n, float* lse, int M, void* stream);
+int coda_b200_cross_entropy_fwd_bwd(void* logits, int64_t ld, const float* lse, const int32_t* target, int ignore_index,
+                                    float* losses, int M, int N, void* stream);
+
 /* Size in bytes of the scratch buffer coda_b200_qknorm_rope_bwd needs. */
 int64_t coda_b200_qknorm_rope_bwd_scratch_bytes(int M, int head_dim);
 

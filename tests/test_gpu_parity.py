@@ -317,3 +317,26 @@ def test_rstd_variants_golden_and_oracle(ck, golden_dir):
     close(preact, rp, what="preact (large)")
     close(ms, rms, tol=1e-3, what="mean square (large)")
     close(v, (xg.float() @ d["weight"].to(DEV)[size_qk:].float().mT) * r2[:, None], what="v (large)")
+
+
+# ------------------------------------------------------------------------------------------------ logits dataflow of the reference
+@pytest.mark.parametrize("name", ["ce_mean", "ce_sum"])
+def test_gemm_lse_and_cross_entropy_fwd_bwd(ck, golden_dir, name):
+    """``gemm_lse`` + ``cross_entropy_fwd_bwd`` chained as in the reference's ``_forward_lse``."""
+    from coda_kernels_b200 import ops_logits as L
+
+    g = load(golden_dir, name)
+    d = g["inputs"]
+    x, w, t = d["x"].to(DEV), d["weight"].to(DEV), d["target"].to(DEV)
+    logits, lses = L.gemm_lse(x, w.mT)
+    ref_logits = x.float() @ w.float().mT
+    close(logits, ref_logits, what="logits")
+    close(lses, g["lse"], tol=LOSS_TOL, what="lse")
+    losses, dlogits = L.cross_entropy_fwd_bwd(logits, lses, t, -100)
+    status_ok(ck)
+    assert dlogits.data_ptr() == logits.data_ptr(), "the gradient overwrites the logits in place"
+    # the target logit is read from the bf16-rounded logits here, as in the reference: looser than the fused path
+    close(losses, g["row_losses"], tol=5e-3, what="row losses")
+    close(dlogits, g["dlogits"], what="dlogits")
+    ignored = t == -100
+    assert (losses[ignored] == 0).all() and (dlogits[ignored].view(torch.int16) == 0).all()
