@@ -32,6 +32,7 @@ struct Options {
   int cta_group = 2;  // 1 = one CTA per tile (128 rows), 2 = CTA pair per tile (256 rows)
   int group_m = 0;    // raster group in tiles; 0 = default
   int max_ctas = 0;   // cap on the persistent grid; 0 = all SMs
+  int tile_n = 0;     // 0 = choose per problem; 128 or 256 forces the column-tile width where both are built
   int dbg_lbo_mn = 0;
   int dbg_sbo_mn = 0;
 };
@@ -177,8 +178,28 @@ int launch_gemm_cfg(const void* a_ptr, long long lda, const void* b_ptr, long lo
   return kOk;
 }
 
-// Dispatch on CTA grouping and operand majors.  kMajors: bit0 = allow A MN-major, bit1 = allow B MN-major.
-template <class Epi, int kAllowMajors>
+// Column-tile width for epilogues that are built for both 128 and 256 columns.  The narrow tile wins when the
+// wide one would leave the last wave of the persistent grid mostly empty (few output tiles) or when N itself is
+// narrow; otherwise the wide tile is kept, since it reads A once per 256 instead of once per 128 output columns.
+inline int choose_tile_n(int M, int N, int cta_group) {
+  const int forced = options().tile_n;
+  if (forced == 128 || forced == 256) return forced;
+  if (N <= 128) return 128;
+  int sms = sm_count();
+  if (options().max_ctas > 0 && options().max_ctas < sms) sms = options().max_ctas;
+  const long long clusters = sms / cta_group > 0 ? sms / cta_group : 1;
+  const long long tiles_m = (M + kBlockM * cta_group - 1) / (kBlockM * cta_group);
+  const long long w256 = (tiles_m * ((N + 255) / 256) + clusters - 1) / clusters;
+  const long long w128 = (tiles_m * ((N + 127) / 128) + clusters - 1) / clusters;
+  // Cost in units of one 256-wide wave.  A 128-wide wave costs about 0.75 of it, not 0.5: with N = 128 each MMA
+  // reads as many operand bytes from shared memory per cycle as the SM can deliver (measured: forcing the narrow
+  // tile on 6144- and 5120-wide outputs lost 10-15 % of a step), so it only pays for narrow or single-wave outputs.
+  return (w128 * 0.75 < w256 * 0.97) ? 128 : 256;
+}
+
+// Dispatch on CTA grouping, operand majors and (if kNarrow) column-tile width.
+// kAllowMajors: bit0 = allow A MN-major, bit1 = allow B MN-major.
+template <class Epi, int kAllowMajors, bool kNarrow = false>
 int launch_gemm(const Operand& A, const Operand& B, int M, int N, int K, const typename Epi::Params& ep, int* status,
                 cudaStream_t stream) {
   if (M <= 0 || N <= 0 || K <= 0) return fail(kBadArgument, "GEMM extents must be positive");
@@ -188,20 +209,30 @@ int launch_gemm(const Operand& A, const Operand& B, int M, int N, int K, const t
   if (!classify(A, M, K, &a_mn, &lda)) return fail(kBadLayout, "A must be contiguous along one of its two dimensions");
   if (!classify(B, N, K, &b_mn, &ldb)) return fail(kBadLayout, "B must be contiguous along one of its two dimensions");
   const bool two = options().cta_group == 2;
-#define CB_LAUNCH(AM, BM)                                                                                          \
-  (two ? launch_gemm_cfg<2, 256, AM, BM, Epi>(A.ptr, lda, B.ptr, ldb, M, N, K, ep, status, stream)                   \
-       : launch_gemm_cfg<1, 256, AM, BM, Epi>(A.ptr, lda, B.ptr, ldb, M, N, K, ep, status, stream))
-  if (!a_mn && !b_mn) return CB_LAUNCH(false, false);
+  bool narrow = false;
+  if constexpr (kNarrow) narrow = choose_tile_n(M, N, two ? 2 : 1) == 128;
+#define CB_LAUNCH_BN(BN, AM, BM)                                                                                   \
+  (two ? launch_gemm_cfg<2, BN, AM, BM, Epi>(A.ptr, lda, B.ptr, ldb, M, N, K, ep, status, stream)                    \
+       : launch_gemm_cfg<1, BN, AM, BM, Epi>(A.ptr, lda, B.ptr, ldb, M, N, K, ep, status, stream))
+#define CB_LAUNCH(AM, BM)                                                \
+  do {                                                                   \
+    if constexpr (kNarrow) {                                             \
+      if (narrow) return CB_LAUNCH_BN(128, AM, BM);                      \
+    }                                                                    \
+    return CB_LAUNCH_BN(256, AM, BM);                                    \
+  } while (0)
+  if (!a_mn && !b_mn) CB_LAUNCH(false, false);
   if constexpr ((kAllowMajors & 2) != 0) {
-    if (!a_mn && b_mn) return CB_LAUNCH(false, true);
+    if (!a_mn && b_mn) CB_LAUNCH(false, true);
   }
   if constexpr ((kAllowMajors & 1) != 0) {
-    if (a_mn && !b_mn) return CB_LAUNCH(true, false);
+    if (a_mn && !b_mn) CB_LAUNCH(true, false);
   }
   if constexpr (kAllowMajors == 3) {
-    if (a_mn && b_mn) return CB_LAUNCH(true, true);
+    if (a_mn && b_mn) CB_LAUNCH(true, true);
   }
 #undef CB_LAUNCH
+#undef CB_LAUNCH_BN
   return fail(kBadLayout, "this fused GEMM needs both operands contiguous along the contraction dimension");
 }
 

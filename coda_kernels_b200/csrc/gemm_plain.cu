@@ -19,6 +19,9 @@ extern "C" int coda_b200_set_option(const char* name, int value) {
     o.group_m = value;
   } else if (!strcmp(name, "max_ctas")) {
     o.max_ctas = value;
+  } else if (!strcmp(name, "tile_n")) {
+    if (value != 0 && value != 128 && value != 256) return fail(kBadArgument, "tile_n must be 0, 128 or 256");
+    o.tile_n = value;
   } else if (!strcmp(name, "dbg_lbo_mn")) {
     o.dbg_lbo_mn = value;
   } else if (!strcmp(name, "dbg_sbo_mn")) {
@@ -42,7 +45,7 @@ int run_store(const void* A, int64_t asm_, int64_t ask, const void* B, int64_t b
   ep.alpha = alpha;
   Operand a{A, asm_, ask};
   Operand b{B, bsn, bsk};
-  return launch_gemm<EpiStore<OutT, kAct>, 3>(a, b, M, N, K, ep, dev_status, static_cast<cudaStream_t>(stream));
+  return launch_gemm<EpiStore<OutT, kAct>, 3, true>(a, b, M, N, K, ep, dev_status, static_cast<cudaStream_t>(stream));
 }
 }  // namespace
 

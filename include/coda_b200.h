@@ -42,6 +42,7 @@ int coda_b200_version(void);
 const char* coda_b200_last_error(void);
 
 /* Tuning / debug switches: "cta_group" (1 or 2), "group_m", "max_ctas",
+ * "tile_n" (0 = automatic, 128, 256; plain and sigmoid GEMMs only),
  * "dbg_lbo_mn", "dbg_sbo_mn".  Returns 0, or CODA_B200_EARG for an unknown name. */
 int coda_b200_set_option(const char* name, int value);
 

@@ -340,3 +340,30 @@ def test_gemm_lse_and_cross_entropy_fwd_bwd(ck, golden_dir, name):
     close(dlogits, g["dlogits"], what="dlogits")
     ignored = t == -100
     assert (losses[ignored] == 0).all() and (dlogits[ignored].view(torch.int16) == 0).all()
+
+
+@pytest.mark.parametrize("cta_group", [1, 2])
+@pytest.mark.parametrize("a_t,b_t", [(False, False), (False, True), (True, True)])
+def test_gemm_narrow_tile(ck, a_t, b_t, cta_group):
+    """The 128-column tile (chosen automatically for narrow or few-tile outputs) forced on, in the three layouts the operators use."""
+    gen = torch.Generator().manual_seed(11)
+    M, K, N = 520, 264, 392
+    A = torch.randn((K, M) if a_t else (M, K), generator=gen).to(torch.bfloat16).to(DEV)
+    B = torch.randn((N, K) if b_t else (K, N), generator=gen).to(torch.bfloat16).to(DEV)
+    Av, Bv = (A.mT if a_t else A), (B.mT if b_t else B)
+    ref = Av.float() @ Bv.float()
+    ck.set_option("cta_group", cta_group)
+    ck.set_option("tile_n", 128)
+    try:
+        out = ck.ops.gemm(Av, Bv)
+        sig = ck.ops.gemm_sigmoid(Av, Bv, out=torch.empty(M, N, dtype=torch.float32, device=DEV))
+        status_ok(ck)
+    finally:
+        ck.set_option("tile_n", 0)
+        ck.set_option("cta_group", 2)
+    close(out, ref, what="bf16 out, 128-column tiles")
+    close(sig, torch.sigmoid(ref), tol=1e-3, what="sigmoid fp32 out, 128-column tiles")
+    # automatic choice: a skinny output (N = 32 gate heads) takes the narrow tile and stays correct
+    W = torch.randn(32, K, generator=gen).to(torch.bfloat16).to(DEV)
+    x = A.mT if a_t else A
+    close(ck.ops.gemm_sigmoid(x, W.mT), torch.sigmoid(x.float() @ W.float().mT), what="skinny sigmoid")
