@@ -291,8 +291,19 @@ def cpu_eager_step(op: str, rows: int, seed_inputs: dict | None = None):
     return fn, algorithmic_flops(op, s)
 
 
+def use_all_host_threads() -> int:
+    """torchrun exports OMP_NUM_THREADS=1; the CPU legs are meant to use every core the process may run on."""
+    try:
+        n = len(os.sched_getaffinity(0))
+    except AttributeError:
+        n = os.cpu_count() or 1
+    torch.set_num_threads(max(n, 1))
+    return torch.get_num_threads()
+
+
 def time_cpu(op: str, rows: int, steps: int, warmup: int) -> tuple[float, float]:
     """Returns (TFLOP/s, seconds per step) of the CPU eager formulation on a ``rows``-row sample."""
+    use_all_host_threads()
     fn, flops = cpu_eager_step(op, rows)
     for _ in range(warmup):
         fn()
