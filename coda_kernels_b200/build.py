@@ -8,6 +8,7 @@ next to this file, so that the binary travels with the source tree.
 
 from __future__ import annotations
 
+import fcntl
 import hashlib
 import os
 import shutil
@@ -72,6 +73,19 @@ def build_library(force: bool = False, verbose: bool = False) -> Path:
         return LIB_PATH
     nvcc = _nvcc()
     OBJ_DIR.mkdir(exist_ok=True)
+    # Several ranks may import the package at once: one builds, the others wait and then find a fresh library.
+    lock = open(OBJ_DIR / ".lock", "w")
+    fcntl.flock(lock, fcntl.LOCK_EX)
+    try:
+        if not force and not is_stale():
+            return LIB_PATH
+        return _build_locked(nvcc, force, verbose)
+    finally:
+        fcntl.flock(lock, fcntl.LOCK_UN)
+        lock.close()
+
+
+def _build_locked(nvcc: str, force: bool, verbose: bool) -> Path:
     header_mtime = max(f.stat().st_mtime for f in list(CSRC.glob("*.cuh")) + [PKG_DIR.parent / "include" / "coda_b200.h"])
 
     def compile_one(src: Path) -> Path:

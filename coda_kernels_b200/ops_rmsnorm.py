@@ -14,7 +14,7 @@ import torch
 from torch import Tensor
 
 from ._lib import check, lib
-from .ops import _BF16, _ce_grad_fixup, _noop_fake, _require, _require_cuda_bf16, _stream, lse_finalize, lse_tiles, status_word
+from .ops import _ce_grad_fixup, _noop_fake, _require, _require_cuda_bf16, _stream, lse_finalize, lse_tiles, status_word
 
 
 def _check_rstd(rstd: Tensor, M: int) -> None:
