@@ -87,10 +87,17 @@ class CodaB200Error(RuntimeError):
     """A C-ABI call rejected its arguments or a CUDA call failed."""
 
 
+# Optional callable run after every successful library call; ``ops`` installs a synchronising device-status check
+# here when CODA_B200_SYNC_STATUS=1 (debug aid: turns an expired device-side wait into an exception at the call site).
+post_call_hook = None
+
+
 def check(rc: int, what: str) -> None:
     if rc != 0:
         msg = lib.coda_b200_last_error()
         raise CodaB200Error(f"{what} failed (code {rc}): {msg.decode() if msg else ''}")
+    if post_call_hook is not None:
+        post_call_hook(what)
 
 
 def set_option(name: str, value: int) -> None:

@@ -122,8 +122,8 @@ __global__ void __launch_bounds__(256) lse_finalize_kernel(const float* __restri
 __global__ void __launch_bounds__(256) ce_fwd_bwd_kernel(__nv_bfloat16* __restrict__ logits, long long ld,
                                                          const float* __restrict__ lse, const int* __restrict__ target,
                                                          int ignore_index, float* __restrict__ losses, int N8) {
-  const int row = blockIdx.y;
-  const int c8 = blockIdx.x * blockDim.x + threadIdx.x;
+  const int row = blockIdx.x;
+  const int c8 = blockIdx.y * blockDim.x + threadIdx.x;
   if (c8 >= N8) return;
   const int col = c8 * 8;
   uint4* ptr = reinterpret_cast<uint4*>(logits + row * ld + col);
@@ -155,32 +155,46 @@ __global__ void __launch_bounds__(256) ce_fwd_bwd_kernel(__nv_bfloat16* __restri
 }
 
 // ------------------------------------------------------------------ softmax-gradient fix-up, in place
+// Rows on grid.x (no 65535 limit), 4096 columns per block: each thread owns two 16-byte pieces 2048 columns apart
+// and has both loads in flight before it computes.
 __global__ void __launch_bounds__(256) ce_grad_fixup_kernel(__nv_bfloat16* __restrict__ P, long long ldp,
                                                             const float* __restrict__ part_max, int tiles_n, int tile_w,
                                                             const float* __restrict__ lse, const int* __restrict__ target,
                                                             int ignore_index, int N8) {
-  const int row = blockIdx.y;
-  const int c8 = blockIdx.x * blockDim.x + threadIdx.x;
-  if (c8 >= N8) return;
-  const int col = c8 * 8;
-  uint4* ptr = reinterpret_cast<uint4*>(P + row * ldp + col);
+  const int row = blockIdx.x;
+  const int c8a = blockIdx.y * 512 + threadIdx.x;
+  const int c8b = c8a + 256;
+  if (c8a >= N8) return;
+  const bool has_b = c8b < N8;
+  __nv_bfloat16* prow = P + row * ldp;
+  uint4* pa = reinterpret_cast<uint4*>(prow + c8a * 8);
+  uint4* pb = reinterpret_cast<uint4*>(prow + c8b * 8);
   const int tgt = target[row];
   if (tgt == ignore_index) {
-    *ptr = make_uint4(0u, 0u, 0u, 0u);
+    *pa = make_uint4(0u, 0u, 0u, 0u);
+    if (has_b) *pb = make_uint4(0u, 0u, 0u, 0u);
     return;
   }
-  const float f = __expf(part_max[static_cast<long long>(row) * tiles_n + col / tile_w] - lse[row]);
-  const uint4 p4 = *ptr;
-  const uint32_t w[4] = {p4.x, p4.y, p4.z, p4.w};
-  uint32_t r[4];
+  const uint4 va = *pa;
+  const uint4 vb = has_b ? *pb : make_uint4(0u, 0u, 0u, 0u);
+  const float l = lse[row];
+  const float* pm = part_max + static_cast<long long>(row) * tiles_n;
+  const float fa = __expf(pm[(c8a * 8) / tile_w] - l);
+  const float fb = has_b ? __expf(pm[(c8b * 8) / tile_w] - l) : 0.f;
+  auto fix = [tgt](const uint4& v, float f, int col) {
+    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+    uint32_t r[4];
 #pragma unroll
-  for (int j = 0; j < 4; ++j) {
-    float2 v = unpack_bf16x2(w[j]);
-    v.x = v.x * f - ((col + 2 * j) == tgt ? 1.0f : 0.0f);
-    v.y = v.y * f - ((col + 2 * j + 1) == tgt ? 1.0f : 0.0f);
-    r[j] = pack_bf16x2(v.x, v.y);
-  }
-  *ptr = make_uint4(r[0], r[1], r[2], r[3]);
+    for (int j = 0; j < 4; ++j) {
+      float2 t = unpack_bf16x2(w[j]);
+      t.x = t.x * f - ((col + 2 * j) == tgt ? 1.0f : 0.0f);
+      t.y = t.y * f - ((col + 2 * j + 1) == tgt ? 1.0f : 0.0f);
+      r[j] = pack_bf16x2(t.x, t.y);
+    }
+    return make_uint4(r[0], r[1], r[2], r[3]);
+  };
+  *pa = fix(va, fa, c8a * 8);
+  if (has_b) *pb = fix(vb, fb, c8b * 8);
 }
 
 // ------------------------------------------------------------------ QK-norm + RoPE backward
@@ -413,9 +427,9 @@ extern "C" int coda_b200_cross_entropy_fwd_bwd(void* logits, int64_t ld, const f
   if (!logits || !lse || !target || !losses) return fail(kBadArgument, "NULL pointer");
   if (M <= 0 || N <= 0 || N % 8 != 0 || ld % 8 != 0 || ld < N || !aligned16(logits))
     return fail(kBadArgument, "logits must be 16-byte aligned, N and ld multiples of 8");
-  if (M > 65535) return fail(kBadArgument, "M above 65535 is not supported by this grid");
   const int N8 = N / 8;
-  dim3 grid((N8 + 255) / 256, M, 1);
+  if ((N8 + 255) / 256 > 65535) return fail(kBadArgument, "N too large for this grid");
+  dim3 grid(M, (N8 + 255) / 256, 1);
   ce_fwd_bwd_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<__nv_bfloat16*>(logits), ld, lse, target,
                                                                         ignore_index, losses, N8);
   return launch_check("cross_entropy_fwd_bwd launch");
@@ -426,11 +440,10 @@ extern "C" int coda_b200_ce_grad_fixup(void* P, int64_t ldp, const float* part_m
   if (!P || !part_max || !lse || !target) return fail(kBadArgument, "NULL pointer");
   if (M <= 0 || N <= 0 || N % 8 != 0 || ldp % 8 != 0 || ldp < N || !aligned16(P))
     return fail(kBadArgument, "P must be 16-byte aligned, N and ldp multiples of 8");
-  if (M > 65535 * 64) return fail(kBadArgument, "M too large for the fix-up grid");
   if (tiles_n != coda_b200_lse_tiles(N)) return fail(kBadArgument, "tiles_n does not match coda_b200_lse_tiles(N)");
   const int N8 = N / 8;
-  dim3 grid((N8 + 255) / 256, M, 1);
-  if (M > 65535) return fail(kBadArgument, "M above 65535 is not supported by the fix-up grid");
+  if ((N8 + 511) / 512 > 65535) return fail(kBadArgument, "N too large for the fix-up grid");
+  dim3 grid(M, (N8 + 511) / 512, 1);
   ce_grad_fixup_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<__nv_bfloat16*>(P), ldp, part_max,
                                                                            tiles_n, 256, lse, target, ignore_index, N8);
   return launch_check("ce_grad_fixup launch");

@@ -11,11 +11,13 @@ memory and the current stream; all arithmetic runs in the library's kernels.
 
 from __future__ import annotations
 
+import os
 from typing import Optional
 
 import torch
 from torch import Tensor
 
+from . import _lib as _lib_module
 from ._lib import check, lib
 
 _BF16 = torch.bfloat16
@@ -39,6 +41,19 @@ def check_device_status(device: Optional[torch.device] = None) -> None:
     if code != 0:
         status_word(device).zero_()
         raise RuntimeError(f"coda_b200 kernel reported device-side error code {code} (a bounded wait expired)")
+
+
+def _sync_status_hook(what: str) -> None:
+    torch.cuda.synchronize()
+    for idx, word in list(_status_words.items()):
+        code = int(word.item())
+        if code != 0:
+            word.zero_()
+            raise RuntimeError(f"coda_b200: device-side error code {code} on cuda:{idx}, detected after {what}")
+
+
+if os.environ.get("CODA_B200_SYNC_STATUS", "0") == "1":
+    _lib_module.post_call_hook = _sync_status_hook
 
 
 def _stream(t: Tensor) -> int:
