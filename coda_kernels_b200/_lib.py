@@ -25,6 +25,7 @@ SIGNATURES = {
     "coda_b200_version": (_I, []),
     "coda_b200_last_error": (c_char_p, []),
     "coda_b200_set_option": (_I, [c_char_p, _I]),
+    "coda_b200_selftest_wait_timeout": (_I, [_P, _L, _P, _P]),
     "coda_b200_gemm": (_I, [_P, _L, _L, _P, _L, _L, _P, _L, _I, _I, _I, _I, _P, _P, _P]),
     "coda_b200_gemm_sigmoid": (_I, [_P, _L, _L, _P, _L, _L, _P, _L, _I, _I, _I, _I, _P, _P]),
     "coda_b200_gemm_swiglu": (_I, [_P, _L, _L, _P, _L, _L, _P, _L, _P, _L, _I, _I, _I, _P, _P]),

@@ -100,22 +100,26 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   return ok != 0;
 }
 
-// Bounded wait.  Returns false if the barrier did not flip in time or some
+// Bounded wait.  Returns false if the barrier did not flip within `timeout_ns` or some
 // other role of this CTA already gave up; `abort_word` is a shared-memory int.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_word, int code) {
+__device__ __forceinline__ bool mbar_wait_for(uint32_t bar, uint32_t parity, volatile int* abort_word, int code,
+                                              unsigned long long timeout_ns) {
   if (mbar_try_wait(bar, parity)) return true;
   const unsigned long long t0 = globaltimer_ns();
   uint32_t spins = 0;
   while (!mbar_try_wait(bar, parity)) {
     if ((++spins & 0xFFu) == 0u) {
       if (*abort_word != 0) return false;
-      if (globaltimer_ns() - t0 > kWaitTimeoutNs) {
+      if (globaltimer_ns() - t0 > timeout_ns) {
         *abort_word = code;
         return false;
       }
     }
   }
   return true;
+}
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_word, int code) {
+  return mbar_wait_for(bar, parity, abort_word, code, kWaitTimeoutNs);
 }
 
 // ---------------------------------------------------------------- TMA

@@ -46,6 +46,13 @@ const char* coda_b200_last_error(void);
  * "dbg_lbo_mn", "dbg_sbo_mn".  Returns 0, or CODA_B200_EARG for an unknown name. */
 int coda_b200_set_option(const char* name, int value);
 
+/* Failure-path self-test (no counterpart in the reference).  Launches one warp
+ * that waits, with the same bounded wait every kernel role uses, on a barrier
+ * that nothing arrives at; after `timeout_us` (1 us .. 1 s) the wait gives up,
+ * the kernel returns normally and dev_status receives a positive code.
+ * waited_us (device int32, may be NULL) receives the time the wait took. */
+int coda_b200_selftest_wait_timeout(int* dev_status, int64_t timeout_us, int* waited_us, void* stream);
+
 /* D[M,N] = alpha * (A[M,K] @ B[K,N]); D row-major with leading dimension ldd,
  * bf16 (d_is_fp32 = 0) or fp32 (1); alpha = device fp32 scalar or NULL.
  * Replaces `coda::_gemm` and `coda::_gemm_scalar_scale_epi`

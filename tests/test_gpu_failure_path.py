@@ -1,0 +1,39 @@
+"""Failure detection without a GPU fault: a device-side wait that nothing satisfies ends by itself within its limit,
+the kernel returns normally, the status word carries the code, Python raises, and the context stays usable."""
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def test_bounded_wait_expires_and_reports():
+    import coda_kernels_b200 as ck
+    from coda_kernels_b200 import _lib, ops
+
+    dev = torch.device(DEV)
+    word = ops.status_word(dev)
+    torch.cuda.synchronize()
+    assert int(word.item()) == 0
+    waited = torch.zeros(1, dtype=torch.int32, device=dev)
+    rc = _lib.lib.coda_b200_selftest_wait_timeout(word.data_ptr(), 2000, waited.data_ptr(), torch.cuda.current_stream().cuda_stream)
+    assert rc == 0, _lib.lib.coda_b200_last_error()
+    torch.cuda.synchronize()  # returns: the wait gave up by itself
+    us = int(waited.item())
+    assert 2000 <= us < 200000, f"the wait should end shortly after its 2 ms limit, took {us} us"
+    assert int(word.item()) > 0
+    with pytest.raises(RuntimeError, match="device-side error code"):
+        ops.check_device_status(dev)
+    assert int(word.item()) == 0, "reading the status clears it"
+    # the context is still healthy: a real operator runs and is correct afterwards
+    x = torch.randn(256, 128, device=dev).to(torch.bfloat16)
+    w = torch.randn(256, 128, device=dev).to(torch.bfloat16)
+    out = ck.ops.gemm(x, w.mT)
+    ref = x.float() @ w.float().mT
+    torch.cuda.synchronize()
+    ops.check_device_status(dev)
+    assert (out.float() - ref).abs().max() <= 2e-2 * ref.abs().max()
+    # bad arguments are refused on the host
+    assert _lib.lib.coda_b200_selftest_wait_timeout(None, 10, None, None) == -1
+    assert _lib.lib.coda_b200_selftest_wait_timeout(word.data_ptr(), 0, None, None) == -1
