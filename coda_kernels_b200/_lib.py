@@ -46,6 +46,12 @@ SIGNATURES = {
     "coda_b200_gemm_lse_logits": (_I, [_P, _L, _L, _P, _L, _L, _P, _P, _L, _P, _P, _I, _I, _I, _P, _P]),
     "coda_b200_lse_reduce": (_I, [_P, _P, _I, _P, _I, _P]),
     "coda_b200_cross_entropy_fwd_bwd": (_I, [_P, _L, _P, _P, _I, _P, _I, _I, _P]),
+    "coda_b200_gemm_residual_partial_rmsnorm": (
+        _I, [_P, _L, _L, _P, _L, _L, _P, _L, _P, _F, _P, _L, _P, _L, _P, _P, _I, _I, _I, _P, _P]),
+    "coda_b200_gemm_swiglu_bwd_zdz": (
+        _I, [_P, _L, _L, _P, _L, _L, _P, _L, _P, _L, _P, _L, _P, _F, _P, _I, _I, _I, _P, _P]),
+    "coda_b200_gemm_residual_partial_rmsnorm_bwd": (
+        _I, [_P, _L, _L, _P, _L, _L, _P, _P, _L, _P, _P, _P, _P, _L, _I, _P, _P, _L, _P, _I, _I, _I, _P, _P]),
     "coda_b200_dswiglu": (_I, [_P, _L, _P, _L, _P, _L, _I, _I, _P]),
     "coda_b200_dsigmoid": (_I, [_P, _L, _I, _P, _L, _P, _L, _I, _I, _P]),
     "coda_b200_qknorm_rope_bwd_scratch_bytes": (_L, [_I, _I]),

@@ -168,6 +168,41 @@ int coda_b200_lse_reduce(const float* part_max, const float* part_sum, int tiles
 int coda_b200_cross_entropy_fwd_bwd(void* logits, int64_t ld, const float* lse, const int32_t* target, int ignore_index,
                                     float* losses, int M, int N, void* stream);
 
+/* GEMMs that sit between the fused-linear operators inside a transformer layer.
+ *
+ * coda_b200_gemm_residual_partial_rmsnorm: pre = A @ B + C, post = pre * weight[col],
+ * rstd[M] = rsqrt(mean_col(pre^2) + eps) from the unrounded sum; C may alias pre or
+ * post.  part_sq is fp32 scratch [M, ceil(N / 256)].  Replaces
+ * `coda::_gemm_residual_partial_rmsnorm_epi` (coda/core/gemm/functional.py:573-652).
+ *
+ * coda_b200_gemm_swiglu_bwd_zdz: acc = A @ B is d(postact) [M, N]; Z is the stored
+ * SwiGLU preact [M, 2N] (gate, up interleaved; may alias dZ).  Writes dZ =
+ * dswiglu(Z, acc) [M, 2N], postact = silu(gate) * up [M, N] and zdz[M] = scale *
+ * sum_col(Z * dZ).  part_zdz is fp32 scratch [M, ceil(N / 256)].  Replaces
+ * `coda::_gemm_swiglu_bwd_zdz_epi(_scaled)` (coda/core/gemm/functional.py:827-952).
+ *
+ * coda_b200_gemm_residual_partial_rmsnorm_bwd: y = alpha * (A @ B) (alpha: device
+ * scalar or NULL), n = pre * rstd[row]; dX = (y * weight[col] - n * zdz[row]) *
+ * rstd[row], added to dX's contents if accumulate != 0; normed = n * weight[col]
+ * (may alias pre); dW[N] fp32 = sum_row(y * n).  part_dw is fp32 scratch
+ * [ceil(M / 32), N].  Replaces `coda::_gemm_residual_partial_rmsnorm_bwd_epi_{store,accum}`
+ * (coda/core/gemm/functional.py:655-824). */
+int coda_b200_gemm_residual_partial_rmsnorm(const void* A, int64_t a_stride_m, int64_t a_stride_k, const void* B,
+                                            int64_t b_stride_k, int64_t b_stride_n, const void* C, int64_t ldc,
+                                            const void* weight, float eps, void* pre, int64_t ld_pre, void* post,
+                                            int64_t ld_post, float* rstd, float* part_sq, int M, int N, int K, int* dev_status,
+                                            void* stream);
+int coda_b200_gemm_swiglu_bwd_zdz(const void* A, int64_t a_stride_m, int64_t a_stride_k, const void* B, int64_t b_stride_k,
+                                  int64_t b_stride_n, const void* Z, int64_t ldz, void* dZ, int64_t ld_dz, void* postact,
+                                  int64_t ld_post, float* zdz, float scale, float* part_zdz, int M, int N, int K,
+                                  int* dev_status, void* stream);
+int coda_b200_gemm_residual_partial_rmsnorm_bwd(const void* A, int64_t a_stride_m, int64_t a_stride_k, const void* B,
+                                                int64_t b_stride_k, int64_t b_stride_n, const void* weight, const void* pre,
+                                                int64_t ld_pre, const float* zdz, const float* rstd, const float* alpha,
+                                                void* dX, int64_t ld_dx, int accumulate, float* dW, void* normed,
+                                                int64_t ld_normed, float* part_dw, int M, int N, int K, int* dev_status,
+                                                void* stream);
+
 /* Size in bytes of the scratch buffer coda_b200_qknorm_rope_bwd needs. */
 int64_t coda_b200_qknorm_rope_bwd_scratch_bytes(int M, int head_dim);
 

@@ -184,6 +184,41 @@ def gemm_rmsnorm_qknorm_rope(A, B, rstd, weight, positions, frequencies, head_di
     return rope_interleaved(normed, cos, sin), preact, ms
 
 
+# ---------------------------------------------------------------------------------------------- GEMMs between the operators
+def gemm_residual_partial_rmsnorm(A, B, C, weight, eps, compute_dtype=torch.float32):
+    """``pre = A @ B + C``, ``post = pre * weight``, ``rstd`` of the unrounded ``pre`` (torch_ops.py:528-549)."""
+    pre = _c(A, compute_dtype) @ _c(B, compute_dtype) + _c(C, compute_dtype)
+    return pre, pre * _c(weight, compute_dtype), torch.rsqrt(pre.square().mean(dim=-1) + eps)
+
+
+def gemm_swiglu_bwd_zdz(A, B, Z, scale=None, compute_dtype=torch.float32):
+    """Down-projection dgrad ``A @ B^T`` through SwiGLU at the stored preact ``Z``: ``(dZ, ZdZ, postact)``
+    with ``ZdZ = scale * sum(Z * dZ)`` (torch_ops.py:466-490)."""
+    dpost = _c(A, compute_dtype) @ _c(B, compute_dtype).mT
+    z = _c(Z, compute_dtype)
+    dz = dswiglu(z, dpost)
+    zdz = (z * dz).sum(dim=-1)
+    if scale is not None:
+        zdz = zdz * scale
+    return dz, zdz, F.silu(z[:, 0::2]) * z[:, 1::2]
+
+
+def gemm_residual_partial_rmsnorm_bwd(A, B, weight, pre, ZdZ, rstd, alpha=None, dX=None, compute_dtype=torch.float32):
+    """The next GEMM's dgrad ``A @ B^T`` (times ``alpha``) through the RMSNorm backward at the stored ``pre`` and
+    ``rstd``: ``(dpre [+ dX], dweight, normed)`` (torch_ops.py:91-113, 552-583)."""
+    grad = _c(A, compute_dtype) @ _c(B, compute_dtype).mT
+    if alpha is not None:
+        grad = grad * _c(alpha, compute_dtype)
+    r = _c(rstd, compute_dtype)[:, None]
+    w = _c(weight, compute_dtype)
+    n = _c(pre, compute_dtype) * r
+    dpre = (grad * w - n * _c(ZdZ, compute_dtype)[:, None]) * r
+    dweight = (grad * n).sum(dim=0)
+    if dX is not None:
+        dpre = dpre + _c(dX, compute_dtype)
+    return dpre, dweight, n * w
+
+
 # ---------------------------------------------------------------------------------------------- fwd + bwd helpers
 def fwd_bwd(fn, inputs: dict, grad_names: list[str], cotangents):
     """Run ``fn(**inputs)`` with autograd on ``grad_names`` and return ``(outputs, grads)``.

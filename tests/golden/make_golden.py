@@ -113,6 +113,37 @@ def rstd_case(name, M, K, Fdim, V, d_, hq, hk, seed):
                 "row_losses": losses, "dlogits": dlogits, "qk_rotated": rot, "qk_preact": preact, "qk_mean_sq": ms})
 
 
+def block_case(name, M, K, N, Fdim, seed):
+    """The GEMMs between the operators: residual + partial RMSNorm (forward, backward) and the SwiGLU dgrad."""
+    g = torch.Generator().manual_seed(seed)
+    rn = lambda *s_, std=1.0: (torch.randn(*s_, generator=g) * std).to(torch.bfloat16)  # noqa: E731
+    A, B, C = rn(M, K), rn(K, N, std=K**-0.5), rn(M, N)
+    weight = (1.0 + 0.1 * torch.randn(N, generator=g)).to(torch.bfloat16)
+    pre, post, rstd = torch_ops.gemm_residual_partial_rmsnorm(A.to(F64), B.to(F64), C.to(F64), weight.to(F64), 1e-5)
+    # backward: dgrad of the next GEMM, A2 [M, K2] @ B2 [N, K2]^T
+    A2, B2 = rn(M, K), rn(N, K, std=K**-0.5)
+    zdz = torch.randn(M, generator=g).to(torch.float32)
+    alpha = torch.tensor(0.37, dtype=torch.float32)
+    dX0 = rn(M, N)
+    pre_bf = pre.to(torch.bfloat16)
+    rstd32 = rstd.to(torch.float32)
+    outs = {}
+    for key, al, dx in (("plain", None, None), ("alpha_accum", alpha, dX0)):
+        dpre, dw, normed = torch_ops.gemm_residual_partial_rmsnorm_bwd(
+            A2.to(F64), B2.to(F64), weight.to(F64), pre_bf.to(F64), zdz.to(F64), rstd32.to(F64),
+            alpha=None if al is None else al.to(F64), dX=None if dx is None else dx.to(F64))
+        outs[key] = {"dX": dpre, "dW": dw, "normed": normed}
+    # swiglu dgrad: A3 [M, K] @ B3 [F, K]^T, Z [M, 2F]
+    A3, B3, Z = rn(M, K), rn(Fdim, K, std=K**-0.5), rn(M, 2 * Fdim)
+    sw = {}
+    for key, sc in (("plain", None), ("scaled", 0.125)):
+        dZ, ZdZ, postact = torch_ops.gemm_swiglu_bwd_zdz(A3.to(F64), B3.to(F64), Z.to(F64), IL, scale=sc)
+        sw[key] = {"dZ": dZ, "ZdZ": ZdZ, "postact": postact}
+    save(name, {"A": A, "B": B, "C": C, "weight": weight, "eps": 1e-5, "pre": pre, "post": post, "rstd": rstd, "A2": A2, "B2": B2,
+                "zdz": zdz, "alpha": alpha, "dX0": dX0, "pre_bf16": pre_bf, "rstd32": rstd32, "bwd": outs, "A3": A3, "B3": B3,
+                "Z": Z, "swiglu_bwd": sw})
+
+
 if __name__ == "__main__":
     torch.manual_seed(0)
     swiglu_case("swiglu_small", 48, 64, 40, seed=1)
@@ -124,3 +155,4 @@ if __name__ == "__main__":
     qk_case("qk_gqa_d128_far", 20, 72, 128, 2, 1, 1, seq=10, seed=7, pos_offset=1 << 20)
     qk_case("qk_mha_d64_fpos", 16, 64, 64, 2, 2, 2, seq=16, seed=8, pos_offset=5, float_pos=True)
     rstd_case("rstd_variants", 24, 64, 24, 264, 64, 2, 1, seed=9)
+    block_case("block_gemms", 45, 64, 72, 40, seed=10)

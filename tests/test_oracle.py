@@ -111,3 +111,24 @@ def test_rstd_variants(golden_dir):
         close(preact, g["qk_preact"], tol)
         close(ms, g["qk_mean_sq"], tol)
     assert torch.allclose(eager.rmsnorm_rstd(g["x"], 1e-5, F64).float(), g["rstd"])
+
+
+def test_block_gemms(golden_dir):
+    """Residual + partial RMSNorm (forward, backward) and the SwiGLU dgrad against the reference's eager ops."""
+    g = load(golden_dir, "block_gemms")
+    for dtype, tol in ((F64, 1e-10), (torch.float32, 5e-5)):
+        pre, post, rstd = eager.gemm_residual_partial_rmsnorm(g["A"], g["B"], g["C"], g["weight"], g["eps"], compute_dtype=dtype)
+        close(pre, g["pre"], tol)
+        close(post, g["post"], tol)
+        close(rstd, g["rstd"], tol)
+        for key, al, dx in (("plain", None, None), ("alpha_accum", g["alpha"], g["dX0"])):
+            dX, dW, normed = eager.gemm_residual_partial_rmsnorm_bwd(
+                g["A2"], g["B2"], g["weight"], g["pre_bf16"], g["zdz"], g["rstd32"], alpha=al, dX=dx, compute_dtype=dtype)
+            close(dX, g["bwd"][key]["dX"], tol)
+            close(dW, g["bwd"][key]["dW"], tol)
+            close(normed, g["bwd"][key]["normed"], tol)
+        for key, sc in (("plain", None), ("scaled", 0.125)):
+            dZ, ZdZ, postact = eager.gemm_swiglu_bwd_zdz(g["A3"], g["B3"], g["Z"], scale=sc, compute_dtype=dtype)
+            close(dZ, g["swiglu_bwd"][key]["dZ"], tol)
+            close(ZdZ, g["swiglu_bwd"][key]["ZdZ"], tol)
+            close(postact, g["swiglu_bwd"][key]["postact"], tol)
