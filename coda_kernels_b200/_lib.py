@@ -52,6 +52,11 @@ SIGNATURES = {
         _I, [_P, _L, _L, _P, _L, _L, _P, _L, _P, _L, _P, _L, _P, _F, _P, _I, _I, _I, _P, _P]),
     "coda_b200_gemm_residual_partial_rmsnorm_bwd": (
         _I, [_P, _L, _L, _P, _L, _L, _P, _P, _L, _P, _P, _P, _P, _L, _I, _P, _P, _L, _P, _I, _I, _I, _P, _P]),
+    "coda_b200_partial_rmsnorm": (_I, [_P, _L, _P, _F, _P, _L, _P, _L, _P, _I, _I, _P]),
+    "coda_b200_gemm_rmsnorm_rope": (_I, [_P, _L, _L, _P, _L, _L, _P, _P, _L, _P, _I, _P, _I, _I, _I, _P, _P]),
+    "coda_b200_rope_bwd_zdz": (_I, [_P, _L, _P, _L, _P, _I, _P, _F, _P, _L, _P, _I, _I, _P]),
+    "coda_b200_gemm_rmsnorm_lse_zdz": (_I, [_P, _L, _L, _P, _L, _L, _P, _P, _L, _P, _P, _P, _P, _P, _I, _I, _I, _P, _P]),
+    "coda_b200_lse_finalize_zdz": (_I, [_P, _P, _P, _I, _P, _P, _I, _P, _P, _P, _I, _P]),
     "coda_b200_dswiglu": (_I, [_P, _L, _P, _L, _P, _L, _I, _I, _P]),
     "coda_b200_dsigmoid": (_I, [_P, _L, _I, _P, _L, _P, _L, _I, _I, _P]),
     "coda_b200_qknorm_rope_bwd_scratch_bytes": (_L, [_I, _I]),

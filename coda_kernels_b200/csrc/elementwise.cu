@@ -95,7 +95,9 @@ __global__ void __launch_bounds__(256) dsigmoid_kernel(const OutT* __restrict__ 
 __global__ void __launch_bounds__(256) lse_finalize_kernel(const float* __restrict__ part_max, const float* __restrict__ part_sum,
                                                            int tiles_n, const int* __restrict__ target,
                                                            const float* __restrict__ target_logit, int ignore_index,
-                                                           float* __restrict__ lse, float* __restrict__ losses, int M) {
+                                                           float* __restrict__ lse, float* __restrict__ losses, int M,
+                                                           const float* __restrict__ part_sz = nullptr,
+                                                           float* __restrict__ zdz = nullptr) {
   const int lane = threadIdx.x & 31;
   const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (row >= M) return;
@@ -114,6 +116,89 @@ __global__ void __launch_bounds__(256) lse_finalize_kernel(const float* __restri
     lse[row] = l;
     if (target != nullptr) losses[row] = (target[row] != ignore_index) ? (l - target_logit[row]) : 0.0f;
   }
+  if (zdz != nullptr) {
+    // sum_j z_j * (softmax_j - onehot_j) = sum_t exp(m_t - lse) * sz_t - z_target; zero for ignored rows
+    const float l = mx + logf(s);
+    const float* pz = part_sz + static_cast<long long>(row) * tiles_n;
+    float a = 0.f;
+    for (int t = lane; t < tiles_n; t += 32) a += pz[t] * __expf(pm[t] - l);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) a += __shfl_xor_sync(0xffffffffu, a, o);
+    if (lane == 0) zdz[row] = (target[row] != ignore_index) ? (a - target_logit[row]) : 0.0f;
+  }
+}
+
+// ------------------------------------------------------------------ partial RMSNorm: one warp per row
+// h = x * weight[col], an optional copy of x, and rstd = rsqrt(mean(x^2) + eps), from one read of x.
+__global__ void __launch_bounds__(256) partial_rmsnorm_kernel(const __nv_bfloat16* __restrict__ x, long long ldx,
+                                                              const __nv_bfloat16* __restrict__ weight, float eps,
+                                                              __nv_bfloat16* __restrict__ residual, long long ld_res,
+                                                              __nv_bfloat16* __restrict__ h, long long ld_h,
+                                                              float* __restrict__ rstd, int M, int N8) {
+  const int lane = threadIdx.x & 31;
+  const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (row >= M) return;
+  float sq = 0.f;
+  for (int c8 = lane; c8 < N8; c8 += 32) {
+    const uint4 xv = *reinterpret_cast<const uint4*>(x + row * ldx + c8 * 8);
+    const uint4 wv = __ldg(reinterpret_cast<const uint4*>(weight + c8 * 8));
+    const uint32_t xw[4] = {xv.x, xv.y, xv.z, xv.w}, ww[4] = {wv.x, wv.y, wv.z, wv.w};
+    uint32_t r[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float2 a = unpack_bf16x2(xw[j]), b = unpack_bf16x2(ww[j]);
+      sq = fmaf(a.x, a.x, fmaf(a.y, a.y, sq));
+      r[j] = pack_bf16x2(a.x * b.x, a.y * b.y);
+    }
+    *reinterpret_cast<uint4*>(h + row * ld_h + c8 * 8) = make_uint4(r[0], r[1], r[2], r[3]);
+    if (residual != nullptr) *reinterpret_cast<uint4*>(residual + row * ld_res + c8 * 8) = xv;
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
+  if (lane == 0) rstd[row] = rsqrtf(sq / static_cast<float>(N8 * 8) + eps);
+}
+
+// ------------------------------------------------------------------ RoPE backward with the row dot: one warp per row
+// dz = R^T dy (pairs (a, b) -> (a c + b s, b c - a s) at the angle of their column), zdz = scale * sum(y * dy).
+__global__ void __launch_bounds__(256) rope_bwd_zdz_kernel(const __nv_bfloat16* __restrict__ y, long long ldy,
+                                                           const __nv_bfloat16* __restrict__ dy, long long ld_dy,
+                                                           const void* __restrict__ positions, int pos_is_float,
+                                                           const float* __restrict__ freq, float scale,
+                                                           __nv_bfloat16* __restrict__ dz, long long ld_dz,
+                                                           float* __restrict__ zdz, int M, int N8) {
+  constexpr float kTwoPi = 6.283185307179586f;
+  const int lane = threadIdx.x & 31;
+  const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (row >= M) return;
+  const float pos = pos_is_float ? reinterpret_cast<const float*>(positions)[row]
+                                 : static_cast<float>(reinterpret_cast<const int*>(positions)[row]);
+  float dot = 0.f;
+  for (int c8 = lane; c8 < N8; c8 += 32) {
+    const uint4 yv = *reinterpret_cast<const uint4*>(y + row * ldy + c8 * 8);
+    const uint4 gv = *reinterpret_cast<const uint4*>(dy + row * ld_dy + c8 * 8);
+    const float4 f0 = __ldg(reinterpret_cast<const float4*>(freq + c8 * 8));
+    const float4 f1 = __ldg(reinterpret_cast<const float4*>(freq + c8 * 8 + 4));
+    const float fr[8] = {f0.x, f0.y, f0.z, f0.w, f1.x, f1.y, f1.z, f1.w};
+    const uint32_t yw[4] = {yv.x, yv.y, yv.z, yv.w}, gw[4] = {gv.x, gv.y, gv.z, gv.w};
+    uint32_t r[4];
+#pragma unroll
+    for (int p = 0; p < 4; ++p) {
+      const float2 yy = unpack_bf16x2(yw[p]), g = unpack_bf16x2(gw[p]);
+      dot = fmaf(yy.x, g.x, fmaf(yy.y, g.y, dot));
+      const float hi = fr[2 * p], lo = fr[2 * p + 1];
+      const float t = pos * hi;
+      const float terr = fmaf(pos, hi, -t);
+      const float l = fmaf(pos, lo, terr);
+      const float frac = (t - rintf(t)) + l;
+      float sn, cs;
+      __sincosf(kTwoPi * frac, &sn, &cs);
+      r[p] = pack_bf16x2(g.x * cs + g.y * sn, g.y * cs - g.x * sn);
+    }
+    *reinterpret_cast<uint4*>(dz + row * ld_dz + c8 * 8) = make_uint4(r[0], r[1], r[2], r[3]);
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
+  if (lane == 0) zdz[row] = dot * scale;
 }
 
 // ------------------------------------------------------------------ cross entropy from stored logits, in place
@@ -411,6 +496,42 @@ extern "C" int coda_b200_lse_finalize(const float* part_max, const float* part_s
   lse_finalize_kernel<<<(M + rows_per_block - 1) / rows_per_block, rows_per_block * 32, 0, static_cast<cudaStream_t>(stream)>>>(
       part_max, part_sum, tiles_n, target, target_logit, ignore_index, lse, losses, M);
   return launch_check("lse_finalize launch");
+}
+
+extern "C" int coda_b200_lse_finalize_zdz(const float* part_max, const float* part_sum, const float* part_sz, int tiles_n,
+                                          const int32_t* target, const float* target_logit, int ignore_index, float* lse,
+                                          float* losses, float* zdz, int M, void* stream) {
+  if (!part_max || !part_sum || !part_sz || !target || !target_logit || !lse || !losses || !zdz) return fail(kBadArgument, "NULL pointer");
+  if (M <= 0 || tiles_n <= 0) return fail(kBadArgument, "M and tiles_n must be positive");
+  const int rows_per_block = 8;
+  lse_finalize_kernel<<<(M + rows_per_block - 1) / rows_per_block, rows_per_block * 32, 0, static_cast<cudaStream_t>(stream)>>>(
+      part_max, part_sum, tiles_n, target, target_logit, ignore_index, lse, losses, M, part_sz, zdz);
+  return launch_check("lse_finalize_zdz launch");
+}
+
+extern "C" int coda_b200_partial_rmsnorm(const void* x, int64_t ldx, const void* weight, float eps, void* residual, int64_t ld_res,
+                                         void* h, int64_t ld_h, float* rstd, int M, int N, void* stream) {
+  if (!x || !weight || !h || !rstd) return fail(kBadArgument, "NULL pointer");
+  if (M <= 0 || N <= 0 || N % 8 || ldx % 8 || ld_h % 8 || ldx < N || ld_h < N) return fail(kBadArgument, "N and leading dimensions must be multiples of 8");
+  if (!aligned16(x) || !aligned16(weight) || !aligned16(h)) return fail(kBadArgument, "pointers must be 16-byte aligned");
+  if (residual != nullptr && (!aligned16(residual) || ld_res % 8 || ld_res < N)) return fail(kBadArgument, "bad residual buffer");
+  partial_rmsnorm_kernel<<<(M + 7) / 8, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(x), ldx, static_cast<const __nv_bfloat16*>(weight), eps, static_cast<__nv_bfloat16*>(residual),
+      ld_res, static_cast<__nv_bfloat16*>(h), ld_h, rstd, M, N / 8);
+  return launch_check("partial_rmsnorm launch");
+}
+
+extern "C" int coda_b200_rope_bwd_zdz(const void* y, int64_t ldy, const void* dy, int64_t ld_dy, const void* positions,
+                                      int pos_is_float, const float* frequencies, float scale, void* dz, int64_t ld_dz, float* zdz,
+                                      int M, int N, void* stream) {
+  if (!y || !dy || !positions || !frequencies || !dz || !zdz) return fail(kBadArgument, "NULL pointer");
+  if (M <= 0 || N <= 0 || N % 8 || ldy % 8 || ld_dy % 8 || ld_dz % 8 || ldy < N || ld_dy < N || ld_dz < N)
+    return fail(kBadArgument, "N and leading dimensions must be multiples of 8");
+  if (!aligned16(y) || !aligned16(dy) || !aligned16(dz) || !aligned16(frequencies)) return fail(kBadArgument, "pointers must be 16-byte aligned");
+  rope_bwd_zdz_kernel<<<(M + 7) / 8, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(y), ldy, static_cast<const __nv_bfloat16*>(dy), ld_dy, positions, pos_is_float, frequencies,
+      scale, static_cast<__nv_bfloat16*>(dz), ld_dz, zdz, M, N / 8);
+  return launch_check("rope_bwd_zdz launch");
 }
 
 extern "C" int coda_b200_lse_reduce(const float* part_max, const float* part_sum, int tiles_n, float* lse, int M, void* stream) {

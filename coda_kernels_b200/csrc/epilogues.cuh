@@ -150,6 +150,7 @@ struct EpiLse {
     const int* target;    // [M] or nullptr (no target pick)
     float* target_logit;  // [M]; written only by the tile holding the target column
     const float* row_scale;  // [M] fp32 or nullptr: logits = acc * row_scale[row] (deferred RMSNorm)
+    float* part_sz;          // [M, tiles_n] or nullptr: sum_j exp(z_j - m) * z_j, for sum_j z_j * dlogit_j
   };
   __device__ static void prologue(const Params&, uint8_t*, int) {}
 
@@ -175,7 +176,8 @@ struct EpiLse {
     // pass 2: exponentials, their sum, target logit, optional store
     const int tgt = (row_ok && p.target != nullptr) ? __ldg(p.target + c.row) : -1;
     const int tcol = tgt - c.n0;  // target column relative to this tile
-    float sum = 0.f, tlogit = 0.f;
+    float sum = 0.f, tlogit = 0.f, sz = 0.f;
+    const bool want_sz = p.part_sz != nullptr;
     __nv_bfloat16* prow = (kStore != kLseStoreNone) ? p.P + static_cast<long long>(c.row) * p.ldp + c.n0 : nullptr;
     const float mxs = mx * kLog2e;
 #pragma unroll 1
@@ -196,6 +198,7 @@ struct EpiLse {
       for (int j = 0; j < 32; ++j) {
         const float e = (j < lim) ? fast_exp2(fmaf(v[j], rsl, -mxs)) : 0.f;
         sum += e;
+        if (want_sz) sz = fmaf(e, v[j] * rs, sz);
         v[j] = (kStore == kLseStoreLogits) ? v[j] * rs : e;
       }
       if (kStore != kLseStoreNone && row_ok) store_row32(prow + ch * 32, v, lim);
@@ -203,6 +206,7 @@ struct EpiLse {
     if (row_ok) {
       p.part_max[static_cast<long long>(c.row) * p.tiles_n + c.tn] = mx;
       p.part_sum[static_cast<long long>(c.row) * p.tiles_n + c.tn] = sum;
+      if (want_sz) p.part_sz[static_cast<long long>(c.row) * p.tiles_n + c.tn] = sz;
       if (tcol >= 0 && tcol < nvalid) p.target_logit[c.row] = tlogit;
     }
   }

@@ -39,6 +39,55 @@ __device__ __forceinline__ void load_colvec32(const __nv_bfloat16* src, float* v
   }
 }
 
+// ------------------------------------------------------------------ RoPE on every column (v columns carry frequency 0)
+// D = rotate(acc * row_scale[row]) with the angle of each adjacent column pair taken from `freq` (hi, lo turns) and
+// the row's position.  Replaces `_gemm_rope_epi` / `_gemm_rmsnorm_rope_epi` (coda/core/gemm/functional.py:955-1062).
+struct EpiRope {
+  struct Params {
+    __nv_bfloat16* D;
+    long long ldd;
+    const float* row_scale;  // [M] or nullptr
+    const void* positions;   // [M] int32 or fp32
+    int pos_is_float;
+    const float* freq;  // [N]
+  };
+  __device__ static void prologue(const Params&, uint8_t*, int) {}
+
+  template <int kBN>
+  __device__ static void run(const Params& p, const EpiCtx& c, uint8_t*) {
+    constexpr float kTwoPi = 6.283185307179586f;
+    const bool row_ok = c.row < c.M;
+    const int safe_row = row_ok ? c.row : 0;
+    const float rs = (p.row_scale != nullptr && row_ok) ? __ldg(p.row_scale + c.row) : 1.0f;
+    const float pos = p.pos_is_float ? __ldg(reinterpret_cast<const float*>(p.positions) + safe_row)
+                                     : static_cast<float>(__ldg(reinterpret_cast<const int*>(p.positions) + safe_row));
+#pragma unroll 1
+    for (int ch = 0; ch < kBN / 32; ++ch) {
+      const int col = c.n0 + ch * 32;
+      if (col >= c.N) break;
+      const int ncols = c.N - col;
+      float v[32];
+      tmem_ld32(c.taddr + ch * 32, v);
+      tmem_ld_wait();
+#pragma unroll
+      for (int j = 0; j < 16; ++j) {
+        float2 f = make_float2(0.f, 0.f);
+        if (2 * j < ncols) f = __ldg(reinterpret_cast<const float2*>(p.freq + col + 2 * j));
+        const float t = pos * f.x;
+        const float terr = fmaf(pos, f.x, -t);
+        const float l = fmaf(pos, f.y, terr);
+        const float frac = (t - rintf(t)) + l;
+        float sn, cs;
+        __sincosf(kTwoPi * frac, &sn, &cs);
+        const float a = v[2 * j] * rs, b = v[2 * j + 1] * rs;
+        v[2 * j] = a * cs - b * sn;
+        v[2 * j + 1] = a * sn + b * cs;
+      }
+      if (row_ok) store_row32(p.D + static_cast<long long>(c.row) * p.ldd + col, v, ncols);
+    }
+  }
+};
+
 // ------------------------------------------------------------------ residual add + partial RMSNorm
 // pre = acc + C;  post = pre * weight[col];  per (row, column tile) sum of pre^2 (fp32, unrounded).  The row's
 // rstd = rsqrt(sum / N + eps) is formed afterwards and applied by the GEMM that consumes `post`.  Replaces

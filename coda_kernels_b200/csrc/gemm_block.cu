@@ -76,6 +76,25 @@ extern "C" int coda_b200_gemm_residual_partial_rmsnorm(const void* A, int64_t a_
   return launch_check("rstd reduce launch");
 }
 
+extern "C" int coda_b200_gemm_rmsnorm_rope(const void* A, int64_t a_stride_m, int64_t a_stride_k, const void* B, int64_t b_stride_k,
+                                           int64_t b_stride_n, const float* rstd, void* D, int64_t ldd, const void* positions,
+                                           int pos_is_float, const float* frequencies, int M, int N, int K, int* dev_status,
+                                           void* stream) {
+  if (!A || !B || !D || !positions || !frequencies) return fail(kBadArgument, "NULL pointer");
+  if (N % 8 || ldd % 8 || ldd < N || !aligned16(D)) return fail(kBadArgument, "D must be 16-byte aligned, N and ldd multiples of 8");
+  if (reinterpret_cast<uintptr_t>(frequencies) & 7u) return fail(kBadArgument, "frequencies must be 8-byte aligned");
+  EpiRope::Params ep;
+  ep.D = static_cast<__nv_bfloat16*>(D);
+  ep.ldd = ldd;
+  ep.row_scale = rstd;
+  ep.positions = positions;
+  ep.pos_is_float = pos_is_float;
+  ep.freq = frequencies;
+  Operand a{A, a_stride_m, a_stride_k};
+  Operand b{B, b_stride_n, b_stride_k};
+  return launch_gemm<EpiRope, 0>(a, b, M, N, K, ep, dev_status, static_cast<cudaStream_t>(stream));
+}
+
 extern "C" int coda_b200_gemm_swiglu_bwd_zdz(const void* A, int64_t a_stride_m, int64_t a_stride_k, const void* B,
                                              int64_t b_stride_k, int64_t b_stride_n, const void* Z, int64_t ldz, void* dZ,
                                              int64_t ld_dz, void* postact, int64_t ld_post, float* zdz, float scale,

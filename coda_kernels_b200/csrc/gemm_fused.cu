@@ -40,10 +40,10 @@ extern "C" int coda_b200_gemm_swiglu(const void* A, int64_t a_stride_m, int64_t 
 
 extern "C" int coda_b200_lse_tiles(int N) { return (N + kTileN - 1) / kTileN; }
 
-extern "C" int coda_b200_gemm_rmsnorm_lse(const void* A, int64_t a_stride_m, int64_t a_stride_k, const void* B,
-                                          int64_t b_stride_k, int64_t b_stride_n, const float* rstd, void* P, int64_t ldp,
-                                          float* part_max, float* part_sum, const int32_t* target, float* target_logit, int M,
-                                          int N, int K, int* dev_status, void* stream) {
+extern "C" int coda_b200_gemm_rmsnorm_lse_zdz(const void* A, int64_t a_stride_m, int64_t a_stride_k, const void* B,
+                                              int64_t b_stride_k, int64_t b_stride_n, const float* rstd, void* P, int64_t ldp,
+                                              float* part_max, float* part_sum, float* part_sz, const int32_t* target,
+                                              float* target_logit, int M, int N, int K, int* dev_status, void* stream) {
   if (!A || !B || !part_max || !part_sum || !target || !target_logit) return fail(kBadArgument, "NULL pointer");
   if (N % 8 != 0) return fail(kBadArgument, "N must be a multiple of 8");
   Operand a{A, a_stride_m, a_stride_k};
@@ -60,6 +60,7 @@ extern "C" int coda_b200_gemm_rmsnorm_lse(const void* A, int64_t a_stride_m, int
     ep.target = target;
     ep.target_logit = target_logit;
     ep.row_scale = rstd;
+    ep.part_sz = part_sz;
     return launch_gemm<EpiLse<kLseStoreProbs>, 0>(a, b, M, N, K, ep, dev_status, static_cast<cudaStream_t>(stream));
   }
   EpiLse<kLseStoreNone>::Params ep;
@@ -71,7 +72,16 @@ extern "C" int coda_b200_gemm_rmsnorm_lse(const void* A, int64_t a_stride_m, int
   ep.target = target;
   ep.target_logit = target_logit;
   ep.row_scale = rstd;
+  ep.part_sz = part_sz;
   return launch_gemm<EpiLse<kLseStoreNone>, 0>(a, b, M, N, K, ep, dev_status, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int coda_b200_gemm_rmsnorm_lse(const void* A, int64_t a_stride_m, int64_t a_stride_k, const void* B,
+                                          int64_t b_stride_k, int64_t b_stride_n, const float* rstd, void* P, int64_t ldp,
+                                          float* part_max, float* part_sum, const int32_t* target, float* target_logit, int M,
+                                          int N, int K, int* dev_status, void* stream) {
+  return coda_b200_gemm_rmsnorm_lse_zdz(A, a_stride_m, a_stride_k, B, b_stride_k, b_stride_n, rstd, P, ldp, part_max, part_sum,
+                                        nullptr, target, target_logit, M, N, K, dev_status, stream);
 }
 
 extern "C" int coda_b200_gemm_lse(const void* A, int64_t a_stride_m, int64_t a_stride_k, const void* B, int64_t b_stride_k,
@@ -98,6 +108,7 @@ extern "C" int coda_b200_gemm_lse_logits(const void* A, int64_t a_stride_m, int6
   ep.target = nullptr;
   ep.target_logit = nullptr;
   ep.row_scale = rstd;
+  ep.part_sz = nullptr;
   Operand a{A, a_stride_m, a_stride_k};
   Operand b{B, b_stride_n, b_stride_k};
   return launch_gemm<EpiLse<kLseStoreLogits>, 0>(a, b, M, N, K, ep, dev_status, static_cast<cudaStream_t>(stream));

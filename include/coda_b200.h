@@ -203,6 +203,40 @@ int coda_b200_gemm_residual_partial_rmsnorm_bwd(const void* A, int64_t a_stride_
                                                 int64_t ld_normed, float* part_dw, int M, int N, int K, int* dev_status,
                                                 void* stream);
 
+/* Pieces the fused Llama-3 layer blocks add on top of the GEMMs above.
+ *
+ * coda_b200_partial_rmsnorm: h = x * weight[col], rstd[M] = rsqrt(mean(x^2) + eps) and,
+ * if residual != NULL, a copy of x, from one read of x [M, N].  Replaces
+ * `partial_rmsnorm` (imported by coda/kernels/blocks/llama3.py:10-13).
+ *
+ * coda_b200_gemm_rmsnorm_rope: D = rotate((A @ B) * rstd[row]) over every adjacent
+ * column pair with `frequencies` fp32 [N] ((hi, lo) turns; zero for v columns) and
+ * `positions` [M]; rstd may be NULL.  Replaces `coda::_gemm_rope_epi` /
+ * `coda::_gemm_rmsnorm_rope_epi` (coda/core/gemm/functional.py:955-1062).
+ *
+ * coda_b200_rope_bwd_zdz: dz = R^T dy for the same angles and zdz[M] = scale *
+ * sum_col(y * dy).  Replaces `rope_bwd_zdz` (coda/core/elementwise/zdz.py:21).
+ *
+ * coda_b200_gemm_rmsnorm_lse_zdz / coda_b200_lse_finalize_zdz: the LSE GEMM and its
+ * per-row reduction with one more partial, from which zdz[M] = sum_col(logit *
+ * dlogit) (0 for ignored rows) is formed without touching the [M, N] buffer.
+ * Replace `gemm_rmsnorm_cross_entropy_fwd_bwd(..., return_zdz=True)`
+ * (imported by coda/kernels/blocks/llama3.py:23-26). */
+int coda_b200_partial_rmsnorm(const void* x, int64_t ldx, const void* weight, float eps, void* residual, int64_t ld_res, void* h,
+                              int64_t ld_h, float* rstd, int M, int N, void* stream);
+int coda_b200_gemm_rmsnorm_rope(const void* A, int64_t a_stride_m, int64_t a_stride_k, const void* B, int64_t b_stride_k,
+                                int64_t b_stride_n, const float* rstd, void* D, int64_t ldd, const void* positions,
+                                int pos_is_float, const float* frequencies, int M, int N, int K, int* dev_status, void* stream);
+int coda_b200_rope_bwd_zdz(const void* y, int64_t ldy, const void* dy, int64_t ld_dy, const void* positions, int pos_is_float,
+                           const float* frequencies, float scale, void* dz, int64_t ld_dz, float* zdz, int M, int N, void* stream);
+int coda_b200_gemm_rmsnorm_lse_zdz(const void* A, int64_t a_stride_m, int64_t a_stride_k, const void* B, int64_t b_stride_k,
+                                   int64_t b_stride_n, const float* rstd, void* P, int64_t ldp, float* part_max, float* part_sum,
+                                   float* part_sz, const int32_t* target, float* target_logit, int M, int N, int K,
+                                   int* dev_status, void* stream);
+int coda_b200_lse_finalize_zdz(const float* part_max, const float* part_sum, const float* part_sz, int tiles_n,
+                               const int32_t* target, const float* target_logit, int ignore_index, float* lse, float* losses,
+                               float* zdz, int M, void* stream);
+
 /* Size in bytes of the scratch buffer coda_b200_qknorm_rope_bwd needs. */
 int64_t coda_b200_qknorm_rope_bwd_scratch_bytes(int M, int head_dim);
 

@@ -219,6 +219,49 @@ def gemm_residual_partial_rmsnorm_bwd(A, B, weight, pre, ZdZ, rstd, alpha=None, 
     return dpre, dweight, n * w
 
 
+# ---------------------------------------------------------------------------------------------- Llama-3 layer blocks
+def _rms_norm(x, weight, eps):
+    return x * torch.rsqrt(x.square().mean(dim=-1, keepdim=True) + eps) * weight
+
+
+def _rope_all_columns(x, positions, frequencies):
+    cos, sin = rope_tables(positions, frequencies)  # frequencies are zero on the v columns: identity there
+    return rope_interleaved(x, cos, sin)
+
+
+def llama3_block_pre(x, w, wn, positions, frequencies, eps, compute_dtype=torch.float32):
+    """``(residual, qkv)``: RMSNorm, QKV projection, RoPE on q and k (benchmarks/backends/torch_blocks,py:219-250)."""
+    xc = _c(x, compute_dtype)
+    qkv = _rms_norm(xc, _c(wn, compute_dtype), eps) @ _c(w, compute_dtype).mT
+    return xc, _rope_all_columns(qkv, positions, frequencies)
+
+
+def _llama3_mlp(x0, y0, w0, w1, w2, wn0, eps, compute_dtype):
+    x1 = _c(x0, compute_dtype) + _c(y0, compute_dtype) @ _c(w0, compute_dtype).mT
+    preact = _rms_norm(x1, _c(wn0, compute_dtype), eps) @ _c(w1, compute_dtype).mT
+    postact = F.silu(preact[:, 0::2]) * preact[:, 1::2]
+    return x1 + postact @ _c(w2, compute_dtype).mT
+
+
+def llama3_block(x0, y0, w0, w1, w2, w3, wn0, wn1, positions, frequencies, eps, compute_dtype=torch.float32):
+    """``(x2, qkv)``: output projection + residual, SwiGLU MLP + residual, next layer's norm + QKV + RoPE
+    (benchmarks/backends/torch_blocks,py:253-314)."""
+    x2 = _llama3_mlp(x0, y0, w0, w1, w2, wn0, eps, compute_dtype)
+    qkv = _rms_norm(x2, _c(wn1, compute_dtype), eps) @ _c(w3, compute_dtype).mT
+    return x2, _rope_all_columns(qkv, positions, frequencies)
+
+
+def llama3_block_post(x0, y0, w0, w1, w2, w3, wn0, wn1, targets, eps, ignore_index=-100, reduction="mean",
+                      compute_dtype=torch.float32):
+    """The loss after the last layer's MLP, final norm and LM head (benchmarks/backends/torch_blocks,py:317-377)."""
+    x2 = _llama3_mlp(x0, y0, w0, w1, w2, wn0, eps, compute_dtype)
+    logits = _rms_norm(x2, _c(wn1, compute_dtype), eps) @ _c(w3, compute_dtype).mT
+    total = F.cross_entropy(logits, targets.long(), ignore_index=ignore_index, reduction="sum")
+    if reduction == "mean":
+        return total / (targets != ignore_index).sum().to(dtype=compute_dtype)
+    return total
+
+
 # ---------------------------------------------------------------------------------------------- fwd + bwd helpers
 def fwd_bwd(fn, inputs: dict, grad_names: list[str], cotangents):
     """Run ``fn(**inputs)`` with autograd on ``grad_names`` and return ``(outputs, grads)``.

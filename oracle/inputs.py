@@ -69,3 +69,28 @@ def qknorm_rope_inputs(M: int, K: int, head_dim: int, hq: int, hk: int, hv: int,
         "x": x, "weight": weight, "gamma": gamma, "positions": positions, "frequencies": frequencies,
         "dq": _randn(g, M, hq * head_dim), "dk": _randn(g, M, hk * head_dim), "dv": _randn(g, M, hv * head_dim),
     }
+
+
+def llama3_block_inputs(M: int, dim: int, ffn: int, head_dim: int, heads: int, kv_heads: int, vocab: int, seq_len: int,
+                        theta: float = 500000.0, seed: int = 0) -> dict:
+    """Inputs of the three Llama-3 layer blocks: residual stream, attention output, nn.Linear-style weights (SwiGLU weight
+    interleaved), norm weights near 1, QKV frequencies that are zero on the v columns, and cotangents."""
+    g = _gen(seed)
+    n_qkv = (heads + 2 * kv_heads) * head_dim
+    p = torch.arange(0, head_dim, 2, dtype=torch.float32)
+    turns = (1.0 / (theta ** (p / head_dim))).to(dtype=torch.float64) / (2.0 * math.pi)
+    hi = turns.to(dtype=torch.float32)
+    lo = (turns - hi.to(dtype=torch.float64)).to(dtype=torch.float32)
+    per_head = torch.stack((hi, lo), dim=1).reshape(-1)
+    frequencies = torch.cat((per_head.repeat(heads + kv_heads), torch.zeros(kv_heads * head_dim))).contiguous()
+    norm = lambda: (1.0 + 0.1 * torch.randn(dim, generator=g)).to(dtype=BF16)  # noqa: E731
+    targets = torch.randint(0, vocab, (M,), generator=g, dtype=torch.int64).to(dtype=torch.int32)
+    targets[::7] = -100
+    return {
+        "x0": _randn(g, M, dim), "y0": _randn(g, M, heads * head_dim),
+        "w_qkv": _randn(g, n_qkv, dim, std=dim**-0.5), "w0": _randn(g, dim, heads * head_dim, std=(heads * head_dim) ** -0.5),
+        "w1": _randn(g, 2 * ffn, dim, std=dim**-0.5), "w2": _randn(g, dim, ffn, std=ffn**-0.5),
+        "w_vocab": _randn(g, vocab, dim, std=dim**-0.5), "wn0": norm(), "wn1": norm(),
+        "positions": (torch.arange(M, dtype=torch.int64) % seq_len).to(dtype=torch.int32), "frequencies": frequencies,
+        "targets": targets, "dx": _randn(g, M, dim), "dqkv": _randn(g, M, n_qkv),
+    }

@@ -144,6 +144,42 @@ def block_case(name, M, K, N, Fdim, seed):
                 "Z": Z, "swiglu_bwd": sw})
 
 
+def llama3_blocks_case(name, M, dim, ffn, head_dim, heads, vocab, seed):
+    """block_pre / block / block_post of a Llama-3 layer from the reference's eager blocks (MHA: that code splits qkv in thirds)."""
+    import importlib.machinery
+    import importlib.util
+
+    # the file's name ends in ",py" (a comma), so it has to be loaded by path with an explicit source loader
+    loader = importlib.machinery.SourceFileLoader("ref_torch_blocks", str(REF / "benchmarks" / "backends" / "torch_blocks,py"))
+    spec = importlib.util.spec_from_loader("ref_torch_blocks", loader)
+    tb = importlib.util.module_from_spec(spec)
+    loader.exec_module(tb)
+    d = synth.llama3_block_inputs(M, dim, ffn, head_dim, heads, heads, vocab, seq_len=M, seed=seed)
+    cos, sin = torch_ops.rope_tables(d["positions"].to(F64), d["frequencies"][:head_dim].to(F64))
+    n_qk = 2 * heads * head_dim
+    out = {"inputs": d, "cfg": {"head_dim": head_dim, "heads": heads, "eps": 1e-5}}
+
+    x, w, wn = leaf(d["x0"]), leaf(d["w_qkv"]), leaf(d["wn0"])
+    res, qk, v = tb.block_pre(x, w, wn, cos, sin, head_dim, IL, 1e-5)
+    grads = torch.autograd.grad((res, qk, v), (x, w, wn), (d["dx"].to(F64), d["dqkv"][:, :n_qk].to(F64), d["dqkv"][:, n_qk:].to(F64)))
+    out["pre"] = {"residual": res.detach(), "qkv": torch.cat((qk, v), dim=1).detach(), "dx": grads[0], "dw": grads[1], "dwn": grads[2]}
+
+    names = ("x0", "y0", "w0", "w1", "w2", "w_qkv", "wn0", "wn1")
+    lv = [leaf(d[n]) for n in names]
+    x2, qk, v = tb.block(*lv, cos, sin, head_dim, IL, IL, 1e-5)
+    grads = torch.autograd.grad((x2, qk, v), lv, (d["dx"].to(F64), d["dqkv"][:, :n_qk].to(F64), d["dqkv"][:, n_qk:].to(F64)))
+    out["block"] = {"x2": x2.detach(), "qkv": torch.cat((qk, v), dim=1).detach(), "grads": dict(zip(names, grads))}
+
+    names = ("x0", "y0", "w0", "w1", "w2", "w_vocab", "wn0", "wn1")
+    for reduction in ("mean", "sum"):
+        lv = [leaf(d[n]) for n in names]
+        lv3 = [lv[0][None], lv[1][None]] + lv[2:]
+        loss = tb.block_post(*lv3, d["targets"][None].long(), IL, 1e-5, F64, -100, reduction)
+        grads = torch.autograd.grad(loss, lv)
+        out[f"post_{reduction}"] = {"loss": loss.detach(), "grads": dict(zip(names, grads))}
+    save(name, out)
+
+
 if __name__ == "__main__":
     torch.manual_seed(0)
     swiglu_case("swiglu_small", 48, 64, 40, seed=1)
@@ -156,3 +192,4 @@ if __name__ == "__main__":
     qk_case("qk_mha_d64_fpos", 16, 64, 64, 2, 2, 2, seq=16, seed=8, pos_offset=5, float_pos=True)
     rstd_case("rstd_variants", 24, 64, 24, 264, 64, 2, 1, seed=9)
     block_case("block_gemms", 45, 64, 72, 40, seed=10)
+    llama3_blocks_case("llama3_blocks", 36, 64, 48, 16, 4, 200, seed=11)

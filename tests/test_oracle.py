@@ -132,3 +132,36 @@ def test_block_gemms(golden_dir):
             close(dZ, g["swiglu_bwd"][key]["dZ"], tol)
             close(ZdZ, g["swiglu_bwd"][key]["ZdZ"], tol)
             close(postact, g["swiglu_bwd"][key]["postact"], tol)
+
+
+def test_llama3_blocks(golden_dir):
+    """The oracle's Llama-3 layer blocks against the reference's eager blocks (forward and every gradient)."""
+    g = load(golden_dir, "llama3_blocks")
+    d = g["inputs"]
+    pos, freq = d["positions"], d["frequencies"]
+    for dtype, tol in ((F64, 1e-9), (torch.float32, 1e-4)):
+        fn = functools.partial(eager.llama3_block_pre, positions=pos, frequencies=freq, eps=1e-5, compute_dtype=dtype)
+        outs, grads = eager.fwd_bwd(fn, {"x": d["x0"].to(dtype), "w": d["w_qkv"].to(dtype), "wn": d["wn0"].to(dtype)}, ["x", "w", "wn"],
+                                    (d["dx"], d["dqkv"]))
+        close(outs[0], g["pre"]["residual"], tol)
+        close(outs[1], g["pre"]["qkv"], tol)
+        close(grads["x"], g["pre"]["dx"], tol)
+        close(grads["w"], g["pre"]["dw"], tol)
+        close(grads["wn"], g["pre"]["dwn"], tol)
+
+        names = ["x0", "y0", "w0", "w1", "w2", "w3", "wn0", "wn1"]
+        src = {"w3": "w_qkv"}
+        fn = functools.partial(eager.llama3_block, positions=pos, frequencies=freq, eps=1e-5, compute_dtype=dtype)
+        outs, grads = eager.fwd_bwd(fn, {n: d[src.get(n, n)].to(dtype) for n in names}, names, (d["dx"], d["dqkv"]))
+        close(outs[0], g["block"]["x2"], tol)
+        close(outs[1], g["block"]["qkv"], tol)
+        for n in names:
+            close(grads[n], g["block"]["grads"][src.get(n, n)], tol)
+
+        src = {"w3": "w_vocab"}
+        for reduction in ("mean", "sum"):
+            fn = functools.partial(eager.llama3_block_post, targets=d["targets"], eps=1e-5, reduction=reduction, compute_dtype=dtype)
+            (loss,), grads = eager.fwd_bwd(fn, {n: d[src.get(n, n)].to(dtype) for n in names}, names, torch.tensor(1.0))
+            close(loss, g[f"post_{reduction}"]["loss"], tol)
+            for n in names:
+                close(grads[n], g[f"post_{reduction}"]["grads"][src.get(n, n)], tol)
