@@ -45,6 +45,8 @@ SHAPES = {
     "sigmoid": {"M": 32768, "K": 5120, "N": 5120},
     "cross_entropy": {"M": 8192, "K": 4096, "V": 128256},
     "qknorm_rope": {"M": 16384, "K": 4096, "head_dim": 128, "hq": 32, "hk": 8, "hv": 8, "seq_len": 4096},
+    # one whole Llama-3-8B layer as the fused block (attention itself sits between two blocks, outside)
+    "llama3_block": {"M": 16384, "dim": 4096, "ffn": 14336, "head_dim": 128, "heads": 32, "kv_heads": 8, "seq_len": 4096},
 }
 
 
@@ -56,6 +58,10 @@ NCU_TRAFFIC = {"swiglu": 3.467e9}
 
 def algorithmic_flops(op: str, s: dict) -> float:
     """Forward + backward GEMM flops (3 GEMMs of 2*M*K*N each); recomputation never counts."""
+    if op == "llama3_block":
+        qd, nqkv = s["heads"] * s["head_dim"], (s["heads"] + 2 * s["kv_heads"]) * s["head_dim"]
+        per_row = s["dim"] * qd + s["dim"] * 2 * s["ffn"] + s["ffn"] * s["dim"] + s["dim"] * nqkv  # o-proj, gate/up, down, next qkv
+        return 3.0 * 2.0 * s["M"] * per_row
     if op == "swiglu":
         n = 2 * s["F"]
     elif op == "sigmoid":
@@ -194,6 +200,12 @@ class Workload:
                 "dv": d["dv"][:, rank * hv * dh : (rank + 1) * hv * dh].contiguous(),
             }
             self.kernels_per_step = 5  # fused GEMM, qk backward, partial fold, dgrad GEMM, wgrad GEMM
+        elif op == "llama3_block":
+            if world != 1:
+                raise SystemExit("the fused block benchmark runs on one GPU")
+            d = inputs.llama3_block_inputs(s["M"], s["dim"], s["ffn"], s["head_dim"], s["heads"], s["kv_heads"], 1024, s["seq_len"])
+            host = {k: d[k] for k in ("x0", "y0", "w0", "w1", "w2", "w_qkv", "wn0", "wn1", "positions", "frequencies", "dx", "dqkv")}
+            self.kernels_per_step = 18  # 12 GEMMs, 2 rstd + 1 zdz row reductions, 2 dweight column reductions, rope backward
         else:
             raise ValueError(op)
         self.host = {k: (v.pin_memory() if pinned_host else v) for k, v in host.items()}
@@ -209,6 +221,14 @@ class Workload:
     def step(self, dev_inputs: dict | None = None):
         """Forward + backward through the public operator API.  Returns the result tensors."""
         ck, d = self.ck, (self.dev if dev_inputs is None else dev_inputs)
+        if self.op == "llama3_block":
+            from coda_kernels_b200.blocks import llama3
+
+            names = ("x0", "y0", "w0", "w1", "w2", "w_qkv", "wn0", "wn1")
+            lv = [d[n].detach().requires_grad_(True) for n in names]
+            x2, qkv = llama3.block(*lv, d["positions"], d["frequencies"], 1e-5)
+            grads = torch.autograd.grad((x2, qkv), lv, (d["dx"], d["dqkv"]))  # d["dx"] is accumulated into, as in training
+            return {"x2": x2, "qkv": qkv, **{"d" + n: g_ for n, g_ in zip(names, grads)}}
         x = d["x"].detach().requires_grad_(True)
         w = d["weight"].detach().requires_grad_(True)
         if self.op == "swiglu":
@@ -250,6 +270,13 @@ class Workload:
     def dominant_kernel(self):
         """(label, callable, flops per launch): the fused forward GEMM of this rank's shard, launched alone."""
         ck, d, s = self.ck, self.dev, self.shape
+        if self.op == "llama3_block":
+            from coda_kernels_b200 import ops_rmsnorm
+
+            h = d["x0"]
+            rstd = torch.ones(h.shape[0], dtype=torch.float32, device=h.device)
+            flops = 2.0 * h.shape[0] * h.shape[1] * d["w1"].shape[0]
+            return "gemm_kernel<EpiSwiGLU> (deferred RMSNorm)", (lambda: ops_rmsnorm.gemm_rmsnorm_swiglu(h, d["w1"].mT, rstd)), flops
         x, w = d["x"], d["weight"]
         flops = 2.0 * x.shape[0] * x.shape[1] * w.shape[0]
         if self.op == "swiglu":
@@ -277,6 +304,11 @@ def cpu_eager_step(op: str, rows: int, seed_inputs: dict | None = None):
     elif op == "sigmoid":
         d = inputs.sigmoid_inputs(rows, s["K"], s["N"])
         fn = lambda: eager.fwd_bwd(eager.linear_sigmoid, {"x": d["x"], "weight": d["weight"]}, ["x", "weight"], d["dout"])
+    elif op == "llama3_block":
+        d = inputs.llama3_block_inputs(rows, s["dim"], s["ffn"], s["head_dim"], s["heads"], s["kv_heads"], 1024, s["seq_len"])
+        names = ["x0", "y0", "w0", "w1", "w2", "w3", "wn0", "wn1"]
+        blk = functools.partial(eager.llama3_block, positions=d["positions"], frequencies=d["frequencies"], eps=1e-5)
+        fn = lambda: eager.fwd_bwd(blk, {n: d[{"w3": "w_qkv"}.get(n, n)] for n in names}, names, (d["dx"], d["dqkv"]))
     elif op == "cross_entropy":
         d = inputs.cross_entropy_inputs(rows, s["K"], s["V"])
         ce = functools.partial(eager.linear_cross_entropy, target=d["target"])
@@ -340,6 +372,7 @@ def workload_name(op: str) -> str:
         "sigmoid": "linear_sigmoid fwd+bwd: x[32768,5120] W[5120,5120]",
         "cross_entropy": "linear_cross_entropy fwd+bwd: x[8192,4096] W[128256,4096], 5% ignored, mean",
         "qknorm_rope": "linear_qknorm_rope fwd+bwd: x[16384,4096] W[6144,4096], GQA 32/8/8 x128, theta 5e5",
+        "llama3_block": "fused Llama-3-8B layer block fwd+bwd: 16384 tokens, dim 4096, ffn 14336, GQA 32/8 x128 (o-proj, MLP, next QKV + RoPE)",
     }[op]
 
 
@@ -548,7 +581,7 @@ def main() -> None:
             "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
             "data": "synthetic",
             "config": {"workload": workload_name(args.op) + (f" [rows reduced to {args.rows}]" if args.rows else ""), **s, "global_batch_tokens": s["M"],
-                       "parallelism": {"swiglu": "column", "sigmoid": "column", "cross_entropy": "vocab", "qknorm_rope": "head"}[args.op] + f"-parallel x{world}",
+                       "parallelism": {"swiglu": "column", "sigmoid": "column", "cross_entropy": "vocab", "qknorm_rope": "head", "llama3_block": "no"}[args.op] + f"-parallel x{world}",
                        "dx_allreduce": bool(args.reduce_dx and world > 1), "cuda_graph": graph is not None,
                        "l2": f"no flush: each step streams {wl.h2d_bytes / 1e6:.0f} MB of inputs plus larger intermediates, above the 126 MB L2"},
             "tokens_per_s": s["M"] / (ms_step * 1e-3),
