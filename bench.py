@@ -43,6 +43,9 @@ FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustain
 SHAPES = {
     "swiglu": {"M": 16384, "K": 4096, "F": 14336},
     "sigmoid": {"M": 32768, "K": 5120, "N": 5120},
+    # the sigmoid configuration read literally: sigmoid(X W_gate) * (X W_val), an extension op (the reference's
+    # linear_sigmoid has no value branch); F = width of each of the two projections
+    "sigmoid_glu": {"M": 32768, "K": 5120, "F": 5120},
     "cross_entropy": {"M": 8192, "K": 4096, "V": 128256},
     "qknorm_rope": {"M": 16384, "K": 4096, "head_dim": 128, "hq": 32, "hk": 8, "hv": 8, "seq_len": 4096},
     # one whole Llama-3-8B layer as the fused block (attention itself sits between two blocks, outside)
@@ -62,7 +65,7 @@ def algorithmic_flops(op: str, s: dict) -> float:
         qd, nqkv = s["heads"] * s["head_dim"], (s["heads"] + 2 * s["kv_heads"]) * s["head_dim"]
         per_row = s["dim"] * qd + s["dim"] * 2 * s["ffn"] + s["ffn"] * s["dim"] + s["dim"] * nqkv  # o-proj, gate/up, down, next qkv
         return 3.0 * 2.0 * s["M"] * per_row
-    if op == "swiglu":
+    if op in ("swiglu", "sigmoid_glu"):
         n = 2 * s["F"]
     elif op == "sigmoid":
         n = s["N"]
@@ -172,7 +175,7 @@ class Workload:
         if rows:
             s["M"] = rows  # reduced-row variant of the same workload (profiling captures)
         self.shape = s
-        if op == "swiglu":
+        if op in ("swiglu", "sigmoid_glu"):
             d = inputs.swiglu_inputs(s["M"], s["K"], s["F"])
             lo, hi = parallel.shard_bounds(2 * s["F"], rank, world, 16)
             host = {"x": d["x"], "weight": d["weight"][lo:hi].contiguous(), "dout": d["dout"][:, lo // 2 : hi // 2].contiguous()}
@@ -231,8 +234,8 @@ class Workload:
             return {"x2": x2, "qkv": qkv, **{"d" + n: g_ for n, g_ in zip(names, grads)}}
         x = d["x"].detach().requires_grad_(True)
         w = d["weight"].detach().requires_grad_(True)
-        if self.op == "swiglu":
-            out = ck.linear_swiglu(x, w)
+        if self.op in ("swiglu", "sigmoid_glu"):
+            out = ck.linear_swiglu(x, w) if self.op == "swiglu" else ck.functional.linear_sigmoid_glu(x, w)
             dx, dw = torch.autograd.grad(out, (x, w), d["dout"])
             return {"out": out, "dx": dx, "dweight": dw}
         if self.op == "sigmoid":
@@ -281,6 +284,8 @@ class Workload:
         flops = 2.0 * x.shape[0] * x.shape[1] * w.shape[0]
         if self.op == "swiglu":
             return "gemm_kernel<EpiSwiGLU>", (lambda: ck.ops.gemm_swiglu(x, w.mT)), flops
+        if self.op == "sigmoid_glu":
+            return "gemm_kernel<EpiSigmoidGLU>", (lambda: ck.functional.linear_sigmoid_glu(x, w)), flops
         if self.op == "sigmoid":
             return "gemm_kernel<EpiStore<sigmoid>>", (lambda: ck.ops.gemm_sigmoid(x, w.mT)), flops
         if self.op == "cross_entropy":
@@ -298,7 +303,10 @@ def cpu_eager_step(op: str, rows: int, seed_inputs: dict | None = None):
     from oracle import eager, inputs
 
     s = dict(SHAPES[op])
-    if op == "swiglu":
+    if op == "sigmoid_glu":
+        d = inputs.swiglu_inputs(rows, s["K"], s["F"])
+        fn = lambda: eager.fwd_bwd(eager.linear_sigmoid_glu, {"x": d["x"], "weight": d["weight"]}, ["x", "weight"], d["dout"])
+    elif op == "swiglu":
         d = inputs.swiglu_inputs(rows, s["K"], s["F"])
         fn = lambda: eager.fwd_bwd(eager.linear_swiglu, {"x": d["x"], "weight": d["weight"]}, ["x", "weight"], d["dout"])
     elif op == "sigmoid":
@@ -372,6 +380,7 @@ def workload_name(op: str) -> str:
         "sigmoid": "linear_sigmoid fwd+bwd: x[32768,5120] W[5120,5120]",
         "cross_entropy": "linear_cross_entropy fwd+bwd: x[8192,4096] W[128256,4096], 5% ignored, mean",
         "qknorm_rope": "linear_qknorm_rope fwd+bwd: x[16384,4096] W[6144,4096], GQA 32/8/8 x128, theta 5e5",
+        "sigmoid_glu": "linear_sigmoid_glu (extension) fwd+bwd: x[32768,5120], W_gate and W_val [5120,5120] interleaved into [10240,5120]",
         "llama3_block": "fused Llama-3-8B layer block fwd+bwd: 16384 tokens, dim 4096, ffn 14336, GQA 32/8 x128 (o-proj, MLP, next QKV + RoPE)",
     }[op]
 
@@ -581,7 +590,7 @@ def main() -> None:
             "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
             "data": "synthetic",
             "config": {"workload": workload_name(args.op) + (f" [rows reduced to {args.rows}]" if args.rows else ""), **s, "global_batch_tokens": s["M"],
-                       "parallelism": {"swiglu": "column", "sigmoid": "column", "cross_entropy": "vocab", "qknorm_rope": "head", "llama3_block": "no"}[args.op] + f"-parallel x{world}",
+                       "parallelism": {"swiglu": "column", "sigmoid": "column", "cross_entropy": "vocab", "qknorm_rope": "head", "llama3_block": "no", "sigmoid_glu": "column"}[args.op] + f"-parallel x{world}",
                        "dx_allreduce": bool(args.reduce_dx and world > 1), "cuda_graph": graph is not None,
                        "l2": f"no flush: each step streams {wl.h2d_bytes / 1e6:.0f} MB of inputs plus larger intermediates, above the 126 MB L2"},
             "tokens_per_s": s["M"] / (ms_step * 1e-3),

@@ -29,6 +29,8 @@ SIGNATURES = {
     "coda_b200_gemm": (_I, [_P, _L, _L, _P, _L, _L, _P, _L, _I, _I, _I, _I, _P, _P, _P]),
     "coda_b200_gemm_sigmoid": (_I, [_P, _L, _L, _P, _L, _L, _P, _L, _I, _I, _I, _I, _P, _P]),
     "coda_b200_gemm_swiglu": (_I, [_P, _L, _L, _P, _L, _L, _P, _L, _P, _L, _I, _I, _I, _P, _P]),
+    "coda_b200_gemm_sigmoid_glu": (_I, [_P, _L, _L, _P, _L, _L, _P, _L, _P, _L, _I, _I, _I, _P, _P]),
+    "coda_b200_dsigmoid_glu": (_I, [_P, _L, _P, _L, _P, _L, _I, _I, _P]),
     "coda_b200_lse_tiles": (_I, [_I]),
     "coda_b200_gemm_lse": (_I, [_P, _L, _L, _P, _L, _L, _P, _L, _P, _P, _P, _P, _I, _I, _I, _P, _P]),
     "coda_b200_lse_finalize": (_I, [_P, _P, _I, _P, _P, _I, _P, _P, _I, _P]),

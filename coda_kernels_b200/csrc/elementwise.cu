@@ -19,6 +19,7 @@ inline int launch_check(const char* what) {
 
 // ------------------------------------------------------------------ dSwiGLU
 // One thread: 8 outputs of dout <-> 16 interleaved (gate, up) values.
+template <bool kSigmoidGate>
 __global__ void __launch_bounds__(256) dswiglu_kernel(const __nv_bfloat16* __restrict__ preact, long long ld_pre,
                                                       const __nv_bfloat16* __restrict__ dout, long long ld_dout,
                                                       __nv_bfloat16* __restrict__ grad, long long ld_grad, int M, int F8) {
@@ -42,8 +43,9 @@ __global__ void __launch_bounds__(256) dswiglu_kernel(const __nv_bfloat16* __res
         const float2 gu = unpack_bf16x2(zw[2 * j + h]);
         const float g = gu.x, u = gu.y;
         const float s = fast_sigmoid(g);
-        const float dg = t[h] * u * (s + g * s * (1.0f - s));
-        const float du = t[h] * g * s;
+        // silu gate: d/dg [g s u] = u (s + g s (1 - s)), d/du = g s;  sigmoid gate: d/dg [s u] = u s (1 - s), d/du = s
+        const float dg = kSigmoidGate ? t[h] * u * s * (1.0f - s) : t[h] * u * (s + g * s * (1.0f - s));
+        const float du = kSigmoidGate ? t[h] * s : t[h] * g * s;
         ow[2 * j + h] = pack_bf16x2(dg, du);
       }
     }
@@ -453,18 +455,31 @@ inline int grid_for(long long total, int block) {
 
 }  // namespace
 
-extern "C" int coda_b200_dswiglu(const void* preact, int64_t ld_pre, const void* dout, int64_t ld_dout, void* grad_pre,
-                                 int64_t ld_grad, int M, int F, void* stream) {
+namespace {
+template <bool kSigmoidGate>
+int run_dgated(const void* preact, int64_t ld_pre, const void* dout, int64_t ld_dout, void* grad_pre, int64_t ld_grad, int M, int F,
+               void* stream) {
   if (!preact || !dout || !grad_pre) return fail(kBadArgument, "NULL pointer");
   if (M <= 0 || F <= 0 || F % 8 != 0) return fail(kBadArgument, "F must be a positive multiple of 8");
   if (ld_pre % 8 || ld_dout % 8 || ld_grad % 8 || ld_pre < 2 * F || ld_grad < 2 * F || ld_dout < F)
     return fail(kBadArgument, "leading dimensions must be multiples of 8 and cover the row");
   if (!aligned16(preact) || !aligned16(dout) || !aligned16(grad_pre)) return fail(kBadArgument, "pointers must be 16-byte aligned");
   const int F8 = F / 8;
-  dswiglu_kernel<<<grid_for(static_cast<long long>(M) * F8, 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+  dswiglu_kernel<kSigmoidGate><<<grid_for(static_cast<long long>(M) * F8, 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const __nv_bfloat16*>(preact), ld_pre, static_cast<const __nv_bfloat16*>(dout), ld_dout,
       static_cast<__nv_bfloat16*>(grad_pre), ld_grad, M, F8);
-  return launch_check("dswiglu launch");
+  return launch_check("gated-activation backward launch");
+}
+}  // namespace
+
+extern "C" int coda_b200_dswiglu(const void* preact, int64_t ld_pre, const void* dout, int64_t ld_dout, void* grad_pre,
+                                 int64_t ld_grad, int M, int F, void* stream) {
+  return run_dgated<false>(preact, ld_pre, dout, ld_dout, grad_pre, ld_grad, M, F, stream);
+}
+
+extern "C" int coda_b200_dsigmoid_glu(const void* preact, int64_t ld_pre, const void* dout, int64_t ld_dout, void* grad_pre,
+                                      int64_t ld_grad, int M, int F, void* stream) {
+  return run_dgated<true>(preact, ld_pre, dout, ld_dout, grad_pre, ld_grad, M, F, stream);
 }
 
 extern "C" int coda_b200_dsigmoid(const void* out, int64_t ld_out, int out_is_fp32, const void* dout, int64_t ld_dout,

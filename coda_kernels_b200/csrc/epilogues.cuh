@@ -78,7 +78,11 @@ struct EpiStore {
 // preact[:, c] = bf16(acc[:, c]); postact[:, j] = bf16(silu(acc[:, 2j]) * acc[:, 2j+1]),
 // both from the unrounded accumulator.  Replaces `_gemm_swiglu_epi`
 // (coda/core/gemm/functional.py:237-258, epilogue coda/core/gemm/epilogues.py:44-47).
-struct EpiSwiGLU {
+// kSigmoidGate selects the gate: silu(gate) * up (SwiGLU, the reference op) or sigmoid(gate) * up (a plain sigmoid
+// gate on a value projection: the "gated projection" reading of the sigmoid benchmark configuration, an extension
+// with no counterpart in the reference).
+template <bool kSigmoidGate>
+struct EpiGated {
   struct Params {
     __nv_bfloat16* preact;  // [M, N]
     long long ld_pre;
@@ -107,7 +111,7 @@ struct EpiSwiGLU {
         const float g = v[2 * j] * rs, u = v[2 * j + 1] * rs;
         v[2 * j] = g;
         v[2 * j + 1] = u;
-        o[j] = g * fast_sigmoid(g) * u;
+        o[j] = kSigmoidGate ? fast_sigmoid(g) * u : g * fast_sigmoid(g) * u;
       }
       if (row_ok) {
         const int ncols = c.N - col;
@@ -127,6 +131,9 @@ struct EpiSwiGLU {
     }
   }
 };
+
+using EpiSwiGLU = EpiGated<false>;
+using EpiSigmoidGLU = EpiGated<true>;
 
 // ------------------------------------------------------------------ log-sum-exp partials (+ optional probability store)
 // Per (row, column-tile): m = max_j acc, s = sum_j exp(acc - m).  The tile that

@@ -11,16 +11,17 @@ constexpr int kTileN = 256;  // column-tile width of every fused GEMM in this fi
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 }  // namespace
 
-extern "C" int coda_b200_gemm_rmsnorm_swiglu(const void* A, int64_t a_stride_m, int64_t a_stride_k, const void* B,
-                                             int64_t b_stride_k, int64_t b_stride_n, const float* rstd, void* preact,
-                                             int64_t ld_pre, void* postact, int64_t ld_post, int M, int N, int K,
-                                             int* dev_status, void* stream) {
+namespace {
+template <class Epi>
+int run_gated(const void* A, int64_t a_stride_m, int64_t a_stride_k, const void* B, int64_t b_stride_k, int64_t b_stride_n,
+              const float* rstd, void* preact, int64_t ld_pre, void* postact, int64_t ld_post, int M, int N, int K, int* dev_status,
+              void* stream) {
   if (!A || !B || !preact || !postact) return fail(kBadArgument, "NULL matrix pointer");
-  if (N % 16 != 0) return fail(kBadArgument, "SwiGLU needs N (= 2F) to be a multiple of 16");
+  if (N % 16 != 0) return fail(kBadArgument, "the gated GEMM needs N (= 2F) to be a multiple of 16");
   if (ld_pre % 8 != 0 || ld_post % 8 != 0 || ld_pre < N || ld_post < N / 2)
     return fail(kBadArgument, "output leading dimensions must be multiples of 8 and cover the row");
   if (!aligned16(preact) || !aligned16(postact)) return fail(kBadArgument, "outputs must be 16-byte aligned");
-  EpiSwiGLU::Params ep;
+  typename Epi::Params ep;
   ep.preact = static_cast<__nv_bfloat16*>(preact);
   ep.ld_pre = ld_pre;
   ep.postact = static_cast<__nv_bfloat16*>(postact);
@@ -28,7 +29,23 @@ extern "C" int coda_b200_gemm_rmsnorm_swiglu(const void* A, int64_t a_stride_m, 
   ep.row_scale = rstd;
   Operand a{A, a_stride_m, a_stride_k};
   Operand b{B, b_stride_n, b_stride_k};
-  return launch_gemm<EpiSwiGLU, 0>(a, b, M, N, K, ep, dev_status, static_cast<cudaStream_t>(stream));
+  return launch_gemm<Epi, 0>(a, b, M, N, K, ep, dev_status, static_cast<cudaStream_t>(stream));
+}
+}  // namespace
+
+extern "C" int coda_b200_gemm_rmsnorm_swiglu(const void* A, int64_t a_stride_m, int64_t a_stride_k, const void* B,
+                                             int64_t b_stride_k, int64_t b_stride_n, const float* rstd, void* preact,
+                                             int64_t ld_pre, void* postact, int64_t ld_post, int M, int N, int K,
+                                             int* dev_status, void* stream) {
+  return run_gated<EpiSwiGLU>(A, a_stride_m, a_stride_k, B, b_stride_k, b_stride_n, rstd, preact, ld_pre, postact, ld_post, M, N, K,
+                              dev_status, stream);
+}
+
+extern "C" int coda_b200_gemm_sigmoid_glu(const void* A, int64_t a_stride_m, int64_t a_stride_k, const void* B, int64_t b_stride_k,
+                                          int64_t b_stride_n, void* preact, int64_t ld_pre, void* postact, int64_t ld_post, int M,
+                                          int N, int K, int* dev_status, void* stream) {
+  return run_gated<EpiSigmoidGLU>(A, a_stride_m, a_stride_k, B, b_stride_k, b_stride_n, nullptr, preact, ld_pre, postact, ld_post, M,
+                                  N, K, dev_status, stream);
 }
 
 extern "C" int coda_b200_gemm_swiglu(const void* A, int64_t a_stride_m, int64_t a_stride_k, const void* B,

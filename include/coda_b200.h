@@ -74,6 +74,17 @@ int coda_b200_gemm_swiglu(const void* A, int64_t a_stride_m, int64_t a_stride_k,
                           int64_t b_stride_n, void* preact, int64_t ld_pre, void* postact, int64_t ld_post, int M, int N,
                           int K, int* dev_status, void* stream);
 
+/* Extension (no counterpart in the reference): the sigmoid-gated projection
+ * sigmoid(x @ W_gate^T) * (x @ W_val^T) with gate / value rows interleaved like the
+ * SwiGLU weight: preact = bf16(A @ B) [M,N], postact[:, j] = sigmoid(acc[:, 2j]) *
+ * acc[:, 2j+1] [M,N/2]; coda_b200_dsigmoid_glu is its backward element-wise pass
+ * (dgate = dout*val*s*(1-s), dval = dout*s). */
+int coda_b200_gemm_sigmoid_glu(const void* A, int64_t a_stride_m, int64_t a_stride_k, const void* B, int64_t b_stride_k,
+                               int64_t b_stride_n, void* preact, int64_t ld_pre, void* postact, int64_t ld_post, int M, int N,
+                               int K, int* dev_status, void* stream);
+int coda_b200_dsigmoid_glu(const void* preact, int64_t ld_pre, const void* dout, int64_t ld_dout, void* grad_pre, int64_t ld_grad,
+                           int M, int F, void* stream);
+
 /* Number of column tiles the LSE epilogue produces for N columns
  * (= second extent of part_max / part_sum). */
 int coda_b200_lse_tiles(int N);

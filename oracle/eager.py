@@ -59,6 +59,13 @@ def linear_sigmoid(x: torch.Tensor, weight: torch.Tensor, compute_dtype: torch.d
     return torch.sigmoid(_c(x, compute_dtype) @ _c(weight, compute_dtype).mT)
 
 
+def linear_sigmoid_glu(x: torch.Tensor, weight: torch.Tensor, compute_dtype: torch.dtype = torch.float32) -> torch.Tensor:
+    """``sigmoid(gate) * value`` with gate / value rows interleaved in ``weight [2N, K]``: the gated-projection reading of the
+    sigmoid benchmark configuration (no counterpart in the reference; same structure as ``linear_swiglu``)."""
+    preact = _c(x, compute_dtype) @ _c(weight, compute_dtype).mT
+    return torch.sigmoid(preact[:, 0::2]) * preact[:, 1::2]
+
+
 # ---------------------------------------------------------------------------------------------- cross entropy
 def linear_cross_entropy(
     x: torch.Tensor,

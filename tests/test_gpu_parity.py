@@ -367,3 +367,21 @@ def test_gemm_narrow_tile(ck, a_t, b_t, cta_group):
     W = torch.randn(32, K, generator=gen).to(torch.bfloat16).to(DEV)
     x = A.mT if a_t else A
     close(ck.ops.gemm_sigmoid(x, W.mT), torch.sigmoid(x.float() @ W.float().mT), what="skinny sigmoid")
+
+
+# ------------------------------------------------------------------------------------------------ extension: sigmoid-gated projection
+@pytest.mark.parametrize("shape", [(333, 264, 136), (1024, 512, 1024)])
+def test_sigmoid_glu_vs_oracle(ck, shape):
+    """``sigmoid(x W_gate^T) * (x W_val^T)``: the gated-projection reading of the sigmoid benchmark configuration."""
+    from coda_kernels_b200.functional.sigmoid_glu import linear_sigmoid_glu
+
+    M, K, N = shape
+    d = inputs.swiglu_inputs(M, K, N)  # same interleaved weight layout and distributions
+    x, w = leaf(d["x"]), leaf(d["weight"])
+    out = linear_sigmoid_glu(x, w)
+    dx, dw = torch.autograd.grad(out, (x, w), d["dout"].to(DEV))
+    status_ok(ck)
+    (ro,), g = eager.fwd_bwd(eager.linear_sigmoid_glu, {"x": d["x"].to(DEV), "weight": d["weight"].to(DEV)}, ["x", "weight"], d["dout"].to(DEV))
+    close(out, ro, what="out")
+    close(dx, g["x"], what="dx")
+    close(dw, g["weight"], what="dweight")
