@@ -54,7 +54,7 @@ SHAPES = {
 
 
 # DRAM bytes per launch of the dominant kernel (dram__bytes_read.sum + dram__bytes_write.sum from one ncu capture).
-# swiglu: 866.9 MB measured at 4096 rows (profiles/gemm_kernels_swiglu_rows4096.md), x4 for the 16384-row launch,
+# swiglu: 866.9 MB measured at 4096 rows (the committed ncu summary of the swiglu GEMMs), x4 for the 16384-row launch,
 # since the traffic grows in proportion to the rows.
 NCU_TRAFFIC = {"swiglu": 3.467e9}
 

@@ -1,8 +1,8 @@
 """Generates the golden vectors under tests/golden/ from the reference's own eager implementation.
 
-Run in a container where the reference tree is mounted (default /root/reference):
+Run where the reference tree is available, passing its path:
 
-    python tests/golden/make_golden.py [/path/to/reference]
+    python tests/golden/make_golden.py /path/to/reference
 
 It imports ``benchmarks/backends/torch_linear.py`` and ``torch_ops.py`` of the
 reference unmodified, evaluates every operator of the hot path forward and
@@ -13,6 +13,7 @@ are committed; the reference itself is never copied.
 
 from __future__ import annotations
 
+import os
 import sys
 from pathlib import Path
 
@@ -20,7 +21,7 @@ import torch
 
 HERE = Path(__file__).resolve().parent
 REPO = HERE.parent.parent
-REF = Path(sys.argv[1]) if len(sys.argv) > 1 else Path("/root/reference")
+REF = Path(sys.argv[1] if len(sys.argv) > 1 else os.environ.get("CODA_REFERENCE", "reference")).resolve()
 sys.path.insert(0, str(REF))
 sys.path.insert(0, str(REPO))
 
