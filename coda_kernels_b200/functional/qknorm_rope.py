@@ -1,64 +1,62 @@
-"""``linear_qknorm_rope``: fused ``[q | k | v]`` projection with per-head RMSNorm and RoPE on q, k.
+"""``linear_qknorm_rope``: the attention input projection with per-head RMSNorm and RoPE applied to q and k.
 
-Same signature and autograd behaviour as coda/kernels/functional/qknorm_rope.py:8-136
-(q and k are two views of one buffer; nine gradients, the last six ``None``).
-Unlike the reference's fused epilogue (coda/core/gemm/epilogues.py:213-215) the
-numbers of q and k heads may differ (GQA), and q, k and v come out of one GEMM
-launch; the backward runs one GEMM for ``dx`` and one for ``dweight`` over the
-concatenated ``[grad_pre | dv]``.
+Drop-in for the reference operator (coda/kernels/functional/qknorm_rope.py:8-136): same nine arguments, ``(q, k, v)``
+returned with ``q`` and ``k`` as two column views of one buffer, nine gradients of which the last six are ``None``.
+
+What differs underneath:
+
+* q, k and v come out of ONE GEMM launch over the whole ``[(hq + hk + hv) * d, K]`` weight.  A 128-column head is
+  local to one epilogue thread, so the mean-square, the normalisation by ``gamma_q`` / ``gamma_k`` and the rotation of
+  adjacent column pairs need no cross-thread traffic; v columns are stored as they are.
+* The numbers of q and k heads may differ (grouped-query attention), which the reference's fused epilogue refuses
+  (coda/core/gemm/epilogues.py:213-215).
+* The backward writes ``[grad_pre | dv]`` into one buffer, so ``dx`` and ``dweight`` are one GEMM each (the reference
+  runs two each and adds the ``dx`` halves through an fp32 partial).
 """
 
+from __future__ import annotations
+
 import torch
+from torch import Tensor
 
 from .._guards import autocast_custom_bwd, autocast_custom_fwd, input_guard
-from ..ops import gemm, gemm_qknorm_rope, qknorm_rope_bwd
+from ..ops import gemm_qknorm_rope, qknorm_rope_bwd
+from ._common import linear_backward
 
 
 class LinearQKNormRope(torch.autograd.Function):
+    """Autograd node of :func:`linear_qknorm_rope`."""
+
     @staticmethod
     @input_guard
     @autocast_custom_fwd
-    def forward(ctx, x, weight, gamma, positions, frequencies, head_dim: int, num_heads_q: int, num_heads_k: int, eps: float):
-        size_q = head_dim * num_heads_q
-        size_qk = head_dim * (num_heads_q + num_heads_k)
-        qk, preact, head_mean_sq, v = gemm_qknorm_rope(
-            x, weight.mT, weight=gamma, positions=positions, frequencies=frequencies, head_dim=head_dim,
-            num_heads_q=num_heads_q, num_heads_k=num_heads_k, eps=eps,
-        )
-        if v is None:
+    def forward(ctx, x: Tensor, weight: Tensor, gamma: Tensor, positions: Tensor, frequencies: Tensor, head_dim: int,
+                num_heads_q: int, num_heads_k: int, eps: float):
+        rotated, preact, head_mean_sq, v = gemm_qknorm_rope(
+            x, weight.mT, gamma, positions, frequencies, head_dim, num_heads_q, num_heads_k, eps)
+        if v is None:  # a weight without v rows
             v = x.new_empty(x.shape[0], 0)
-        q, k = qk.split((size_q, size_qk - size_q), dim=-1)
-        ctx.head_dim = head_dim
-        ctx.num_heads_q = num_heads_q
-        ctx.num_heads_k = num_heads_k
-        ctx.eps = eps
+        ctx.cfg = (head_dim, num_heads_q, num_heads_k, eps)
         ctx.save_for_backward(x, weight, gamma, positions, frequencies, preact, head_mean_sq)
-        return q, k, v
+        width_q = head_dim * num_heads_q
+        # two views of `rotated`: the backward receives their gradients separately anyway
+        return rotated[:, :width_q], rotated[:, width_q:], v
 
     @staticmethod
     @input_guard
     @autocast_custom_bwd
-    def backward(ctx, dq, dk, dv):
+    def backward(ctx, grad_q: Tensor, grad_k: Tensor, grad_v: Tensor):
         x, weight, gamma, positions, frequencies, preact, head_mean_sq = ctx.saved_tensors
-        grad, dgamma = qknorm_rope_bwd(
-            dq=dq, dk=dk, dv=dv if dv.shape[1] > 0 else None, x=preact, head_mean_sq=head_mean_sq, gamma=gamma,
-            pos=positions, freq=frequencies, head_dim=ctx.head_dim, num_heads_q=ctx.num_heads_q,
-            num_heads_k=ctx.num_heads_k, eps=ctx.eps,
-        )
-        dx = gemm(grad, weight)  # ([grad_pre | dv]) @ W: the two row blocks of W accumulate in fp32
-        dweight = gemm(grad.mT, x)
-        return dx, dweight, dgamma.to(dtype=gamma.dtype), None, None, None, None, None, None
+        head_dim, num_heads_q, num_heads_k, eps = ctx.cfg
+        has_v = grad_v.shape[1] > 0
+        grad_all, dgamma = qknorm_rope_bwd(grad_q, grad_k, grad_v if has_v else None, preact, head_mean_sq, gamma, positions,
+                                           frequencies, head_dim, num_heads_q, num_heads_k, eps)
+        dx, dweight = linear_backward(grad_all, x, weight, ctx.needs_input_grad[0], ctx.needs_input_grad[1])
+        return (dx, dweight, dgamma.to(dtype=gamma.dtype)) + (None,) * 6
 
 
-def linear_qknorm_rope(
-    x: torch.Tensor,
-    weight: torch.Tensor,
-    gamma: torch.Tensor,
-    positions: torch.Tensor,
-    frequencies: torch.Tensor,
-    head_dim: int,
-    num_heads_q: int,
-    num_heads_k: int,
-    eps: float,
-) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+def linear_qknorm_rope(x: Tensor, weight: Tensor, gamma: Tensor, positions: Tensor, frequencies: Tensor, head_dim: int,
+                       num_heads_q: int, num_heads_k: int, eps: float) -> tuple[Tensor, Tensor, Tensor]:
+    """``x [M, K]``; ``weight`` rows ``[q | k | v]``; ``gamma [2 * head_dim] = [gamma_q | gamma_k]``; ``positions [M]`` int32 or
+    fp32; ``frequencies [(hq + hk) * head_dim]`` fp32 (hi, lo) turns per rotary pair.  Returns ``(q, k, v)``."""
     return LinearQKNormRope.apply(x, weight, gamma, positions, frequencies, head_dim, num_heads_q, num_heads_k, eps)

@@ -1,37 +1,50 @@
-"""``linear_sigmoid``: ``sigmoid(x @ weight^T)``.
+"""``linear_sigmoid(x, weight, out_dtype=None)``: ``sigmoid(x @ weight^T)``.
 
-Same signature and autograd behaviour as coda/kernels/functional/sigmoid.py:7-46:
-the backward uses the saved (rounded) output, and the third gradient is ``None``.
+Drop-in for the reference operator (coda/kernels/functional/sigmoid.py:7-46).  The output dtype defaults to the input's;
+fp32 is the other supported choice.  The backward differentiates through the *stored* (rounded) output, as the
+reference does, and returns ``None`` for ``out_dtype``.
+
+Forward is one launch (GEMM with the sigmoid in its epilogue; a 128-column tile is picked automatically when ``weight``
+has few rows, e.g. one gate per attention head).  Backward is one HBM-bound pass ``dout * out * (1 - out)`` followed by
+the two GEMMs of :func:`linear_backward`.
 """
 
+from __future__ import annotations
+
+from typing import Optional
+
 import torch
+from torch import Tensor
 
 from .._guards import autocast_custom_bwd, autocast_custom_fwd, input_guard
-from ..ops import dsigmoid_backward, gemm, gemm_sigmoid
+from ..ops import dsigmoid_backward, gemm_sigmoid
+from ._common import linear_backward
 
 
 class LinearSigmoid(torch.autograd.Function):
+    """Autograd node of :func:`linear_sigmoid`; saves ``(x, weight, out)``."""
+
     @staticmethod
     @input_guard
     @autocast_custom_fwd
-    def forward(ctx, x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype | None) -> torch.Tensor:
-        if out_dtype is None:
-            out_dtype = x.dtype
-        out = torch.empty(x.shape[0], weight.shape[0], dtype=out_dtype, device=x.device)
-        gemm_sigmoid(x, weight.mT, out=out)
-        ctx.save_for_backward(x, weight, out)
-        return out
+    def forward(ctx, x: Tensor, weight: Tensor, out_dtype: Optional[torch.dtype]) -> Tensor:
+        rows, features = x.shape[0], weight.shape[0]
+        result = x.new_empty((rows, features), dtype=x.dtype if out_dtype is None else out_dtype)
+        gemm_sigmoid(x, weight.mT, out=result)
+        ctx.save_for_backward(x, weight, result)
+        return result
 
     @staticmethod
     @input_guard
     @autocast_custom_bwd
-    def backward(ctx, dout: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor, None]:
-        x, weight, out = ctx.saved_tensors
-        grad_pre = dsigmoid_backward(out, dout.to(dtype=x.dtype))
-        dx = gemm(grad_pre, weight)
-        dweight = gemm(grad_pre.mT, x)
+    def backward(ctx, grad_out: Tensor):
+        x, weight, result = ctx.saved_tensors
+        need_dx, need_dw = ctx.needs_input_grad[:2]
+        grad_pre = dsigmoid_backward(result, grad_out.to(dtype=x.dtype))
+        dx, dweight = linear_backward(grad_pre, x, weight, need_dx, need_dw)
         return dx, dweight, None
 
 
-def linear_sigmoid(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype | None = None) -> torch.Tensor:
+def linear_sigmoid(x: Tensor, weight: Tensor, out_dtype: Optional[torch.dtype] = None) -> Tensor:
+    """``x [M, K]``, ``weight [N, K]`` -> ``sigmoid(x @ weight^T)`` of shape ``[M, N]``."""
     return LinearSigmoid.apply(x, weight, out_dtype)

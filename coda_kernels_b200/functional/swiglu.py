@@ -1,34 +1,45 @@
-"""``linear_swiglu``: ``silu(x @ W_gate^T) * (x @ W_up^T)`` with one interleaved weight.
+"""``linear_swiglu(x, weight)``: the gated MLP up-projection, ``silu(x @ W_gate^T) * (x @ W_up^T)``.
 
-Same signature and autograd behaviour as coda/kernels/functional/swiglu.py:8-30:
-``weight`` is ``[2F, K]`` with gate row ``j`` at ``2j`` and up row ``j`` at ``2j+1``.
+Drop-in for the operator of the same name in the reference (coda/kernels/functional/swiglu.py:8-30): one weight of
+shape ``[2F, K]`` whose even rows are the gate projection and whose odd rows are the up projection, bf16 in and out.
+
+Forward is ONE kernel launch: the tcgen05 GEMM whose epilogue reads each (gate, up) pair from adjacent accumulator
+columns of one thread, writes the bf16 pre-activation (kept for the backward) and the activated product.  Backward is
+one HBM-bound pass that turns (pre-activation, dout) into the pre-activation gradient, then the two GEMMs of
+:func:`linear_backward`.
 """
 
+from __future__ import annotations
+
 import torch
+from torch import Tensor
 
 from .._guards import autocast_custom_bwd, autocast_custom_fwd, input_guard
-from ..ops import dswiglu_backward, gemm, gemm_swiglu
+from ..ops import dswiglu_backward, gemm_swiglu
+from ._common import linear_backward
 
 
 class LinearSwiGLU(torch.autograd.Function):
+    """Autograd node of :func:`linear_swiglu`; saves ``(x, weight, preact)``."""
+
     @staticmethod
     @input_guard
     @autocast_custom_fwd
-    def forward(ctx, x: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
-        preact, out = gemm_swiglu(x, weight.mT)
-        ctx.save_for_backward(x, weight, preact)
-        return out
+    def forward(ctx, x: Tensor, weight: Tensor) -> Tensor:
+        # weight.mT is a view: the kernel consumes the [2F, K] rows as a K-major B operand
+        saved_preact, activated = gemm_swiglu(x, weight.mT)
+        ctx.save_for_backward(x, weight, saved_preact)
+        return activated
 
     @staticmethod
     @input_guard
     @autocast_custom_bwd
-    def backward(ctx, dout: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
-        x, weight, preact = ctx.saved_tensors
-        grad_pre = dswiglu_backward(preact, dout)
-        dx = gemm(grad_pre, weight)  # [M, 2F] @ [2F, K]: weight consumed MN-major, no transpose copy
-        dweight = gemm(grad_pre.mT, x)  # [2F, M] @ [M, K]: both operands MN-major
-        return dx, dweight
+    def backward(ctx, grad_out: Tensor):
+        x, weight, saved_preact = ctx.saved_tensors
+        need_dx, need_dw = ctx.needs_input_grad[:2]
+        return linear_backward(dswiglu_backward(saved_preact, grad_out), x, weight, need_dx, need_dw)
 
 
-def linear_swiglu(x: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
+def linear_swiglu(x: Tensor, weight: Tensor) -> Tensor:
+    """``x [M, K]``, ``weight [2F, K]`` (gate row ``j`` at ``2j``, up row ``j`` at ``2j + 1``) -> ``[M, F]``."""
     return LinearSwiGLU.apply(x, weight)
