@@ -36,18 +36,19 @@ class LinearQKNormRope(torch.autograd.Function):
             x, weight.mT, gamma, positions, frequencies, head_dim, num_heads_q, num_heads_k, eps)
         if v is None:  # a weight without v rows
             v = x.new_empty(x.shape[0], 0)
-        ctx.cfg = (head_dim, num_heads_q, num_heads_k, eps)
+        ctx.head_dim, ctx.num_heads_q, ctx.num_heads_k, ctx.eps = head_dim, num_heads_q, num_heads_k, eps
         ctx.save_for_backward(x, weight, gamma, positions, frequencies, preact, head_mean_sq)
         width_q = head_dim * num_heads_q
         # two views of `rotated`: the backward receives their gradients separately anyway
-        return rotated[:, :width_q], rotated[:, width_q:], v
+        q, k = rotated.split((width_q, rotated.shape[1] - width_q), dim=-1)
+        return q, k, v
 
     @staticmethod
     @input_guard
     @autocast_custom_bwd
     def backward(ctx, grad_q: Tensor, grad_k: Tensor, grad_v: Tensor):
         x, weight, gamma, positions, frequencies, preact, head_mean_sq = ctx.saved_tensors
-        head_dim, num_heads_q, num_heads_k, eps = ctx.cfg
+        head_dim, num_heads_q, num_heads_k, eps = ctx.head_dim, ctx.num_heads_q, ctx.num_heads_k, ctx.eps
         has_v = grad_v.shape[1] > 0
         grad_all, dgamma = qknorm_rope_bwd(grad_q, grad_k, grad_v if has_v else None, preact, head_mean_sq, gamma, positions,
                                            frequencies, head_dim, num_heads_q, num_heads_k, eps)
