@@ -39,7 +39,8 @@ class LinearQKNormRope(torch.autograd.Function):
         ctx.head_dim, ctx.num_heads_q, ctx.num_heads_k, ctx.eps = head_dim, num_heads_q, num_heads_k, eps
         ctx.save_for_backward(x, weight, gamma, positions, frequencies, preact, head_mean_sq)
         width_q = head_dim * num_heads_q
-        # two views of `rotated`: the backward receives their gradients separately anyway
+        # two views of `rotated` (the backward receives their gradients separately anyway); `split` rather than two
+        # slices: with slices the outputs came back wrong under torch.compile(fullgraph=True)
         q, k = rotated.split((width_q, rotated.shape[1] - width_q), dim=-1)
         return q, k, v
 
