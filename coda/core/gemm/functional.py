@@ -26,17 +26,11 @@ from coda_kernels_b200.ops_block import (  # noqa: F401
 
 
 def gemm(A: Tensor, B: Tensor, out: Optional[Tensor] = None, C: Optional[Tensor] = None) -> Tensor:
-    """``out = A @ B (+ C)`` (coda/core/gemm/functional.py:54-69).  With ``C`` the product is taken in fp32 and the
-    addition is a plain tensor add: the B200 operators never need this form (they run one GEMM over concatenated
-    operands instead), it exists for callers written against the reference."""
-    if C is None:
-        return _ops.gemm(A, B, out=out)
-    acc = _ops.gemm(A, B, out_dtype=torch.float32)
-    acc.add_(C)
-    if out is None:
-        return acc.to(dtype=A.dtype)
-    out.copy_(acc)
-    return out
+    """``out = A @ B (+ C)`` (coda/core/gemm/functional.py:54-69); ``C`` is added to the accumulator in the GEMM's epilogue."""
+    if C is not None:
+        assert C.shape == (A.shape[0], B.shape[1])
+        C = C if C.stride(-1) == 1 else C.contiguous()
+    return _ops.gemm(A, B, out=out, C=C)
 
 
 def gemm_scalar_scale(A: Tensor, B: Tensor, alpha: Tensor, out: Optional[Tensor] = None) -> Tensor:

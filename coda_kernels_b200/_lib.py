@@ -27,6 +27,7 @@ SIGNATURES = {
     "coda_b200_set_option": (_I, [c_char_p, _I]),
     "coda_b200_selftest_wait_timeout": (_I, [_P, _L, _P, _P]),
     "coda_b200_gemm": (_I, [_P, _L, _L, _P, _L, _L, _P, _L, _I, _I, _I, _I, _P, _P, _P]),
+    "coda_b200_gemm_add": (_I, [_P, _L, _L, _P, _L, _L, _P, _L, _I, _P, _L, _I, _I, _I, _I, _P, _P, _P]),
     "coda_b200_gemm_sigmoid": (_I, [_P, _L, _L, _P, _L, _L, _P, _L, _I, _I, _I, _I, _P, _P]),
     "coda_b200_gemm_swiglu": (_I, [_P, _L, _L, _P, _L, _L, _P, _L, _P, _L, _I, _I, _I, _P, _P]),
     "coda_b200_gemm_sigmoid_glu": (_I, [_P, _L, _L, _P, _L, _L, _P, _L, _P, _L, _I, _I, _I, _P, _P]),
@@ -116,3 +117,9 @@ def check(rc: int, what: str) -> None:
 
 def set_option(name: str, value: int) -> None:
     check(lib.coda_b200_set_option(name.encode(), int(value)), f"set_option({name})")
+
+
+# CODA_B200_OPTIONS="name=value,name=value": library options applied at import (same names as coda_b200_set_option).
+for _item in filter(None, (s.strip() for s in os.environ.get("CODA_B200_OPTIONS", "").split(","))):
+    _name, _, _value = _item.partition("=")
+    set_option(_name.strip(), int(_value))

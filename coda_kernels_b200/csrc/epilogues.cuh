@@ -3,10 +3,18 @@
 // consecutive fp32 columns, so gate/up pairs, whole attention heads and the
 // row-wise max / sum-exp of a tile are all thread-local: no shuffles needed.
 //
+// Output path: TMEM -> registers -> fused math -> the warp's staging ring in
+// shared memory (swizzled so that the 16-byte pieces of 8 neighbouring rows
+// fall into different banks) -> one TMA store per 32-row x 32-column sub-tile,
+// clipped by the hardware at the matrix edges.  The TMEM load of chunk i+1 is
+// issued before the math of chunk i.  Each Params carries `use_tma`; with 0 the
+// epilogue writes with per-thread 16-byte global stores instead (kept as the
+// comparison path and for callers whose output cannot be described by a
+// tensor map).
+//
 // Each epilogue provides
-//   struct Params                         plain-old-data kernel argument
-//   static void prologue(p, scratch, tid) once per CTA, before the role split
-//   template <int kBN> static void run(p, ctx, scratch)   once per tile per epilogue thread
+//   struct Params                          plain-old-data kernel argument (holds the output tensor maps)
+//   template <int kBN> static void run(p, ctx)   once per tile per epilogue thread
 #pragma once
 
 #include "gemm_core.cuh"
@@ -37,40 +45,160 @@ __device__ __forceinline__ void store_row32(float* dst, const float* v, int ncol
   }
 }
 
+// ------------------------------------------------------------------ staging ring + TMA store
+// Address of 16-byte piece `piece` of row `row` inside a staged sub-tile whose rows are kRowBytes long, in the
+// swizzle mode a tensor map with that inner box width uses (32-, 64- or 128-byte swizzle: the piece index is XORed
+// with the address bits three positions above it).  `tile` must be aligned to 8 rows (256 / 512 / 1024 bytes).
+template <int kRowBytes>
+__device__ __forceinline__ uint32_t stage_addr(uint32_t tile, int row, int piece) {
+  static_assert(kRowBytes == 32 || kRowBytes == 64 || kRowBytes == 128, "row width of a staged sub-tile");
+  if constexpr (kRowBytes == 128) return tile + row * 128 + ((piece ^ (row & 7)) << 4);
+  else if constexpr (kRowBytes == 64) return tile + row * 64 + ((piece ^ ((row >> 1) & 3)) << 4);
+  else return tile + row * 32 + ((piece ^ ((row >> 2) & 1)) << 4);
+}
+
+// kCount consecutive values of this lane's row as bf16 (kCount = 32: 64-byte rows, 16: 32-byte rows).
+template <int kCount>
+__device__ __forceinline__ void stage_row_bf16(uint32_t tile, int lane, const float* v) {
+#pragma unroll
+  for (int j = 0; j < kCount / 8; ++j)
+    st_shared_v4(stage_addr<kCount * 2>(tile, lane, j), pack_bf16x2(v[j * 8 + 0], v[j * 8 + 1]), pack_bf16x2(v[j * 8 + 2], v[j * 8 + 3]),
+                 pack_bf16x2(v[j * 8 + 4], v[j * 8 + 5]), pack_bf16x2(v[j * 8 + 6], v[j * 8 + 7]));
+}
+// 32 consecutive fp32 values of this lane's row (128-byte rows).
+__device__ __forceinline__ void stage_row_f32(uint32_t tile, int lane, const float* v) {
+#pragma unroll
+  for (int j = 0; j < 8; ++j)
+    st_shared_v4(stage_addr<128>(tile, lane, j), __float_as_uint(v[j * 4]), __float_as_uint(v[j * 4 + 1]),
+                 __float_as_uint(v[j * 4 + 2]), __float_as_uint(v[j * 4 + 3]));
+}
+__device__ __forceinline__ void stage_row(uint32_t tile, int lane, const float* v, __nv_bfloat16*) { stage_row_bf16<32>(tile, lane, v); }
+__device__ __forceinline__ void stage_row(uint32_t tile, int lane, const float* v, float*) { stage_row_f32(tile, lane, v); }
+
+// Claim the next slot of the warp's ring: the TMA store that last read it (two groups ago) must have finished reading.
+__device__ __forceinline__ uint32_t ring_acquire(const EpiCtx& c) {
+  if (c.lane == 0) tma_store_wait_read<kRingSlots - 1>();
+  __syncwarp();
+  return c.ring + c.slot * kRingSlotBytes;
+}
+// Every lane has written its row: make the writes visible to the TMA engine.  Lane 0 then issues the stores.
+__device__ __forceinline__ void ring_publish() {
+  fence_proxy_async_smem();
+  __syncwarp();
+}
+// One TMA store of a staged sub-tile to rows row0 .. row0+31, columns from x (issued by lane 0).  A warp whose rows all
+// lie below the matrix issues nothing.
+__device__ __forceinline__ void store_tile(const EpiCtx& c, const CUtensorMap* m, uint32_t tile, int x) {
+  if (c.row0 < c.M) tma_store_2d(m, tile, x, c.row0);
+}
+// Close the bulk group of this slot (lane 0) and move on.
+__device__ __forceinline__ void ring_commit(EpiCtx& c) {
+  if (c.lane == 0) tma_store_commit();
+  c.slot = (c.slot + 1 == kRingSlots) ? 0u : c.slot + 1;
+}
+
+// Calls f(ch, v) for ch = 0 .. n-1 with v = accumulator columns [32 ch, 32 ch + 32) of this thread's row.  Two
+// register buffers: the TMEM load of chunk ch+1 is in flight while f works on chunk ch.  `n` is warp-uniform.
+template <class F>
+__device__ __forceinline__ void for_chunks(uint32_t taddr, int n, F&& f) {
+  if (n <= 0) return;
+  float va[32], vb[32];
+  tmem_ld32(taddr, va);
+#pragma unroll 1
+  for (int ch = 0; ch < n; ch += 2) {
+    tmem_ld_wait();
+    if (ch + 1 < n) tmem_ld32(taddr + (ch + 1) * 32, vb);
+    f(ch, va);
+    if (ch + 1 < n) {
+      tmem_ld_wait();
+      if (ch + 2 < n) tmem_ld32(taddr + (ch + 2) * 32, va);
+      f(ch + 1, vb);
+    }
+  }
+}
+
+// Number of 32-column chunks of a kBN-wide tile starting at column n0 that hold at least one valid column.
+template <int kBN>
+__device__ __forceinline__ int valid_chunks(int n0, int N) {
+  const int left = N - n0;
+  return left >= kBN ? kBN / 32 : (left + 31) / 32;
+}
+
+// 32 consecutive elements of a second [M, N] operand row (bf16 or fp32) as fp32; pieces beyond `ncols` read as zero.
+__device__ __forceinline__ void load_row32_any(const void* base, int is_fp32, long long elem_off, float* v, int ncols, bool row_ok) {
+  if (is_fp32) {
+    const float* src = static_cast<const float*>(base) + elem_off;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      float4 f = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (row_ok && j * 4 < ncols) f = *reinterpret_cast<const float4*>(src + j * 4);
+      v[j * 4] = f.x; v[j * 4 + 1] = f.y; v[j * 4 + 2] = f.z; v[j * 4 + 3] = f.w;
+    }
+  } else {
+    const __nv_bfloat16* src = static_cast<const __nv_bfloat16*>(base) + elem_off;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      uint4 u = make_uint4(0u, 0u, 0u, 0u);
+      if (row_ok && j * 8 < ncols) u = *reinterpret_cast<const uint4*>(src + j * 8);
+      const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const float2 f = unpack_bf16x2(w[k]);
+        v[j * 8 + 2 * k] = f.x;
+        v[j * 8 + 2 * k + 1] = f.y;
+      }
+    }
+  }
+}
+
 // ------------------------------------------------------------------ plain / sigmoid
-// D = act(alpha * acc).  Replaces the reference's `_gemm`, `_gemm_scalar_scale_epi`
-// and `_gemm_sigmoid_epi` (coda/core/gemm/functional.py:35-51, 94-113, 199-217).
+// D = act(alpha * acc + C).  Replaces the reference's `_gemm`, the `C=` form of `gemm` (quack_gemm_add),
+// `_gemm_scalar_scale_epi` and `_gemm_sigmoid_epi` (coda/core/gemm/functional.py:35-69, 94-113, 199-217).
 enum class Act { kNone, kSigmoid };
 
 template <typename OutT, Act kAct>
 struct EpiStore {
   struct Params {
+    alignas(64) CUtensorMap tm_d;  // D as [M, N], box 32 x 32
     OutT* D;
     long long ldd;
     const float* alpha;  // device scalar or nullptr (= 1)
+    const void* C;       // [M, N] addend (bf16 or fp32) or nullptr; may alias D
+    long long ldc;
+    int c_is_fp32;
+    int use_tma;
   };
-  __device__ static void prologue(const Params&, uint8_t*, int) {}
 
   template <int kBN>
-  __device__ static void run(const Params& p, const EpiCtx& c, uint8_t*) {
+  __device__ static void run(const Params& p, EpiCtx& c) {
     const float alpha = p.alpha ? __ldg(p.alpha) : 1.0f;
     const bool row_ok = c.row < c.M;
     OutT* drow = p.D + static_cast<long long>(c.row) * p.ldd + c.n0;
-#pragma unroll 1
-    for (int ch = 0; ch < kBN / 32; ++ch) {
+    for_chunks(c.taddr, valid_chunks<kBN>(c.n0, c.N), [&](int ch, float* v) {
       const int col = c.n0 + ch * 32;
-      if (col >= c.N) break;  // warp-uniform
-      float v[32];
-      tmem_ld32(c.taddr + ch * 32, v);
-      tmem_ld_wait();
+      if (p.C != nullptr) {
+        float t[32];
+        load_row32_any(p.C, p.c_is_fp32, static_cast<long long>(c.row) * p.ldc + col, t, c.N - col, row_ok);
 #pragma unroll
-      for (int j = 0; j < 32; ++j) {
-        float x = v[j] * alpha;
-        if constexpr (kAct == Act::kSigmoid) x = fast_sigmoid(x);
-        v[j] = x;
+        for (int j = 0; j < 32; ++j) v[j] = fmaf(v[j], alpha, t[j]);
+      } else {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] *= alpha;
       }
-      if (row_ok) store_row32(drow + ch * 32, v, c.N - col);
-    }
+      if constexpr (kAct == Act::kSigmoid) {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] = fast_sigmoid(v[j]);
+      }
+      if (p.use_tma) {
+        const uint32_t tile = ring_acquire(c);
+        stage_row(tile, c.lane, v, static_cast<OutT*>(nullptr));
+        ring_publish();
+        if (c.lane == 0) store_tile(c, &p.tm_d, tile, col);
+        ring_commit(c);
+      } else if (row_ok) {
+        store_row32(drow + ch * 32, v, c.N - col);
+      }
+    });
   }
 };
 
@@ -84,27 +212,24 @@ struct EpiStore {
 template <bool kSigmoidGate>
 struct EpiGated {
   struct Params {
+    alignas(64) CUtensorMap tm_pre;   // preact as [M, N], box 32 x 32
+    alignas(64) CUtensorMap tm_post;  // postact as [M, N/2], box 16 x 32
     __nv_bfloat16* preact;  // [M, N]
     long long ld_pre;
     __nv_bfloat16* postact;  // [M, N/2]
     long long ld_post;
     const float* row_scale;  // [M] fp32 or nullptr: acc is multiplied by row_scale[row] first (deferred RMSNorm)
+    int use_tma;
   };
-  __device__ static void prologue(const Params&, uint8_t*, int) {}
 
   template <int kBN>
-  __device__ static void run(const Params& p, const EpiCtx& c, uint8_t*) {
+  __device__ static void run(const Params& p, EpiCtx& c) {
     const bool row_ok = c.row < c.M;
     const float rs = (p.row_scale != nullptr && row_ok) ? __ldg(p.row_scale + c.row) : 1.0f;
     __nv_bfloat16* pre = p.preact + static_cast<long long>(c.row) * p.ld_pre + c.n0;
     __nv_bfloat16* post = p.postact + static_cast<long long>(c.row) * p.ld_post + c.n0 / 2;
-#pragma unroll 1
-    for (int ch = 0; ch < kBN / 32; ++ch) {
+    for_chunks(c.taddr, valid_chunks<kBN>(c.n0, c.N), [&](int ch, float* v) {
       const int col = c.n0 + ch * 32;
-      if (col >= c.N) break;
-      float v[32];
-      tmem_ld32(c.taddr + ch * 32, v);
-      tmem_ld_wait();
       float o[16];
 #pragma unroll
       for (int j = 0; j < 16; ++j) {
@@ -113,7 +238,17 @@ struct EpiGated {
         v[2 * j + 1] = u;
         o[j] = kSigmoidGate ? fast_sigmoid(g) * u : g * fast_sigmoid(g) * u;
       }
-      if (row_ok) {
+      if (p.use_tma) {
+        const uint32_t tile = ring_acquire(c);  // [preact 32 x 64 B | postact 32 x 32 B]
+        stage_row_bf16<32>(tile, c.lane, v);
+        stage_row_bf16<16>(tile + 2048, c.lane, o);
+        ring_publish();
+        if (c.lane == 0) {
+          store_tile(c, &p.tm_pre, tile, col);
+          store_tile(c, &p.tm_post, tile + 2048, col / 2);
+        }
+        ring_commit(c);
+      } else if (row_ok) {
         const int ncols = c.N - col;
         store_row32(pre + ch * 32, v, ncols);
 #pragma unroll
@@ -128,7 +263,7 @@ struct EpiGated {
           }
         }
       }
-    }
+    });
   }
 };
 
@@ -149,6 +284,7 @@ constexpr int kLseStoreNone = 0, kLseStoreProbs = 1, kLseStoreLogits = 2;
 template <int kStore>
 struct EpiLse {
   struct Params {
+    alignas(64) CUtensorMap tm_p;  // P as [M, N], box 32 x 32 (unused for kLseStoreNone)
     __nv_bfloat16* P;  // [M, N] or nullptr
     long long ldp;
     float* part_max;  // [M, tiles_n]
@@ -158,28 +294,30 @@ struct EpiLse {
     float* target_logit;  // [M]; written only by the tile holding the target column
     const float* row_scale;  // [M] fp32 or nullptr: logits = acc * row_scale[row] (deferred RMSNorm)
     float* part_sz;          // [M, tiles_n] or nullptr: sum_j exp(z_j - m) * z_j, for sum_j z_j * dlogit_j
+    int use_tma;
   };
-  __device__ static void prologue(const Params&, uint8_t*, int) {}
 
   template <int kBN>
-  __device__ static void run(const Params& p, const EpiCtx& c, uint8_t*) {
+  __device__ static void run(const Params& p, EpiCtx& c) {
     const bool row_ok = c.row < c.M;
     const int nvalid = min(kBN, c.N - c.n0);  // valid columns in this tile (>= 1)
+    const int nch = (nvalid + 31) / 32;
     constexpr float kLog2e = 1.4426950408889634f;
     const float rs = (p.row_scale != nullptr && row_ok) ? __ldg(p.row_scale + c.row) : 1.0f;
-    // pass 1: row maximum over the tile
+    // pass 1: row maximum over the tile (of the raw accumulator; the row scale is positive)
     float mx = -INFINITY;
-#pragma unroll 1
-    for (int ch = 0; ch < kBN / 32; ++ch) {
-      if (ch * 32 >= nvalid) break;
-      float v[32];
-      tmem_ld32(c.taddr + ch * 32, v);
-      tmem_ld_wait();
+    for_chunks(c.taddr, nch, [&](int ch, float* v) {
       const int lim = nvalid - ch * 32;
+      if (lim >= 32) {
 #pragma unroll
-      for (int j = 0; j < 32; ++j)
-        if (j < lim) mx = fmaxf(mx, v[j] * rs);
-    }
+        for (int j = 0; j < 32; ++j) mx = fmaxf(mx, v[j]);
+      } else {
+#pragma unroll
+        for (int j = 0; j < 32; ++j)
+          if (j < lim) mx = fmaxf(mx, v[j]);
+      }
+    });
+    mx *= rs;
     // pass 2: exponentials, their sum, target logit, optional store
     const int tgt = (row_ok && p.target != nullptr) ? __ldg(p.target + c.row) : -1;
     const int tcol = tgt - c.n0;  // target column relative to this tile
@@ -187,12 +325,8 @@ struct EpiLse {
     const bool want_sz = p.part_sz != nullptr;
     __nv_bfloat16* prow = (kStore != kLseStoreNone) ? p.P + static_cast<long long>(c.row) * p.ldp + c.n0 : nullptr;
     const float mxs = mx * kLog2e;
-#pragma unroll 1
-    for (int ch = 0; ch < kBN / 32; ++ch) {
-      if (ch * 32 >= nvalid) break;
-      float v[32];
-      tmem_ld32(c.taddr + ch * 32, v);
-      tmem_ld_wait();
+    const float rsl = rs * kLog2e;
+    for_chunks(c.taddr, nch, [&](int ch, float* v) {
       const int lim = nvalid - ch * 32;
       const int trel = tcol - ch * 32;
       if (trel >= 0 && trel < 32) {
@@ -200,7 +334,6 @@ struct EpiLse {
         for (int j = 0; j < 32; ++j)
           if (j == trel) tlogit = v[j] * rs;
       }
-      const float rsl = rs * kLog2e;
 #pragma unroll
       for (int j = 0; j < 32; ++j) {
         const float e = (j < lim) ? fast_exp2(fmaf(v[j], rsl, -mxs)) : 0.f;
@@ -208,8 +341,18 @@ struct EpiLse {
         if (want_sz) sz = fmaf(e, v[j] * rs, sz);
         v[j] = (kStore == kLseStoreLogits) ? v[j] * rs : e;
       }
-      if (kStore != kLseStoreNone && row_ok) store_row32(prow + ch * 32, v, lim);
-    }
+      if constexpr (kStore != kLseStoreNone) {
+        if (p.use_tma) {
+          const uint32_t tile = ring_acquire(c);
+          stage_row_bf16<32>(tile, c.lane, v);
+          ring_publish();
+          if (c.lane == 0) store_tile(c, &p.tm_p, tile, c.n0 + ch * 32);
+          ring_commit(c);
+        } else if (row_ok) {
+          store_row32(prow + ch * 32, v, lim);
+        }
+      }
+    });
     if (row_ok) {
       p.part_max[static_cast<long long>(c.row) * p.tiles_n + c.tn] = mx;
       p.part_sum[static_cast<long long>(c.row) * p.tiles_n + c.tn] = sum;
@@ -232,6 +375,9 @@ struct EpiLse {
 template <int kHD>
 struct EpiQKNormRope {
   struct Params {
+    alignas(64) CUtensorMap tm_qk;   // qk as [M, size_qk], box 32 x 32
+    alignas(64) CUtensorMap tm_pre;  // preact as [M, size_qk], box 32 x 32
+    alignas(64) CUtensorMap tm_v;    // v as [M, size_v], box 32 x 32 (unused without v columns)
     __nv_bfloat16* qk;  // [M, size_qk]
     long long ld_qk;
     __nv_bfloat16* preact;  // [M, size_qk]
@@ -246,17 +392,18 @@ struct EpiQKNormRope {
     int hq, hk;
     float eps;
     const float* row_scale;  // [M] fp32 or nullptr: q, k (statistic and output) and v use acc * row_scale[row]; preact keeps acc
+    int use_tma;
   };
-  __device__ static void prologue(const Params&, uint8_t*, int) {}
 
   template <int kBN>
-  __device__ static void run(const Params& p, const EpiCtx& c, uint8_t*) {
+  __device__ static void run(const Params& p, EpiCtx& c) {
     const bool row_ok = c.row < c.M;
     const int safe_row = row_ok ? c.row : 0;
     const float pos = p.pos_is_float ? __ldg(reinterpret_cast<const float*>(p.positions) + safe_row)
                                      : static_cast<float>(__ldg(reinterpret_cast<const int*>(p.positions) + safe_row));
     const int nheads_qk = p.hq + p.hk;
     constexpr float kTwoPi = 6.283185307179586f;
+    constexpr int kChunks = kHD / 32;
     const float rs = (p.row_scale != nullptr && row_ok) ? __ldg(p.row_scale + c.row) : 1.0f;
 #pragma unroll 1
     for (int h = 0; h < kBN / kHD; ++h) {
@@ -266,28 +413,29 @@ struct EpiQKNormRope {
       const uint32_t t0 = c.taddr + h * kHD;
       if (head >= nheads_qk) {
         // v head: plain bf16 store
-        __nv_bfloat16* vrow = p.v + static_cast<long long>(c.row) * p.ld_v + (col0 - nheads_qk * kHD);
-#pragma unroll 1
-        for (int ch = 0; ch < kHD / 32; ++ch) {
-          float v[32];
-          tmem_ld32(t0 + ch * 32, v);
-          tmem_ld_wait();
+        const int vcol0 = col0 - nheads_qk * kHD;
+        __nv_bfloat16* vrow = p.v + static_cast<long long>(c.row) * p.ld_v + vcol0;
+        for_chunks(t0, kChunks, [&](int ch, float* v) {
 #pragma unroll
           for (int j = 0; j < 32; ++j) v[j] *= rs;
-          if (row_ok) store_row32(vrow + ch * 32, v, 32);
-        }
+          if (p.use_tma) {
+            const uint32_t tile = ring_acquire(c);
+            stage_row_bf16<32>(tile, c.lane, v);
+            ring_publish();
+            if (c.lane == 0) store_tile(c, &p.tm_v, tile, vcol0 + ch * 32);
+            ring_commit(c);
+          } else if (row_ok) {
+            store_row32(vrow + ch * 32, v, 32);
+          }
+        });
         continue;
       }
       // pass 1: mean square of the head
       float ss = 0.f;
-#pragma unroll 1
-      for (int ch = 0; ch < kHD / 32; ++ch) {
-        float v[32];
-        tmem_ld32(t0 + ch * 32, v);
-        tmem_ld_wait();
+      for_chunks(t0, kChunks, [&](int, float* v) {
 #pragma unroll
         for (int j = 0; j < 32; ++j) ss = fmaf(v[j], v[j], ss);
-      }
+      });
       const float ms = ss * (1.0f / kHD) * rs * rs;  // statistic of acc * row_scale
       const float r = rsqrtf(ms + p.eps) * rs;
       if (row_ok) p.mean_sq[static_cast<long long>(c.row) * nheads_qk + head] = ms;
@@ -295,12 +443,14 @@ struct EpiQKNormRope {
       __nv_bfloat16* prow = p.preact + static_cast<long long>(c.row) * p.ld_pre + col0;
       __nv_bfloat16* orow = p.qk + static_cast<long long>(c.row) * p.ld_qk + col0;
       // pass 2: normalise, rotate, store
-#pragma unroll 1
-      for (int ch = 0; ch < kHD / 32; ++ch) {
-        float v[32];
-        tmem_ld32(t0 + ch * 32, v);
-        tmem_ld_wait();
-        if (row_ok) store_row32(prow + ch * 32, v, 32);
+      for_chunks(t0, kChunks, [&](int ch, float* v) {
+        uint32_t tile = 0;
+        if (p.use_tma) {
+          tile = ring_acquire(c);  // [preact 32 x 64 B | rotated 32 x 64 B]
+          stage_row_bf16<32>(tile, c.lane, v);
+        } else if (row_ok) {
+          store_row32(prow + ch * 32, v, 32);
+        }
 #pragma unroll
         for (int j = 0; j < 16; ++j) {
           const int e = ch * 32 + 2 * j;  // element index inside the head
@@ -317,8 +467,18 @@ struct EpiQKNormRope {
           v[2 * j] = y0 * cs - y1 * sn;
           v[2 * j + 1] = y0 * sn + y1 * cs;
         }
-        if (row_ok) store_row32(orow + ch * 32, v, 32);
-      }
+        if (p.use_tma) {
+          stage_row_bf16<32>(tile + 2048, c.lane, v);
+          ring_publish();
+          if (c.lane == 0) {
+            store_tile(c, &p.tm_pre, tile, col0 + ch * 32);
+            store_tile(c, &p.tm_qk, tile + 2048, col0 + ch * 32);
+          }
+          ring_commit(c);
+        } else if (row_ok) {
+          store_row32(orow + ch * 32, v, 32);
+        }
+      });
     }
   }
 };

@@ -44,31 +44,27 @@ __device__ __forceinline__ void load_colvec32(const __nv_bfloat16* src, float* v
 // the row's position.  Replaces `_gemm_rope_epi` / `_gemm_rmsnorm_rope_epi` (coda/core/gemm/functional.py:955-1062).
 struct EpiRope {
   struct Params {
+    alignas(64) CUtensorMap tm_d;  // D as [M, N], box 32 x 32
     __nv_bfloat16* D;
     long long ldd;
     const float* row_scale;  // [M] or nullptr
     const void* positions;   // [M] int32 or fp32
     int pos_is_float;
     const float* freq;  // [N]
+    int use_tma;
   };
-  __device__ static void prologue(const Params&, uint8_t*, int) {}
 
   template <int kBN>
-  __device__ static void run(const Params& p, const EpiCtx& c, uint8_t*) {
+  __device__ static void run(const Params& p, EpiCtx& c) {
     constexpr float kTwoPi = 6.283185307179586f;
     const bool row_ok = c.row < c.M;
     const int safe_row = row_ok ? c.row : 0;
     const float rs = (p.row_scale != nullptr && row_ok) ? __ldg(p.row_scale + c.row) : 1.0f;
     const float pos = p.pos_is_float ? __ldg(reinterpret_cast<const float*>(p.positions) + safe_row)
                                      : static_cast<float>(__ldg(reinterpret_cast<const int*>(p.positions) + safe_row));
-#pragma unroll 1
-    for (int ch = 0; ch < kBN / 32; ++ch) {
+    for_chunks(c.taddr, valid_chunks<kBN>(c.n0, c.N), [&](int ch, float* v) {
       const int col = c.n0 + ch * 32;
-      if (col >= c.N) break;
       const int ncols = c.N - col;
-      float v[32];
-      tmem_ld32(c.taddr + ch * 32, v);
-      tmem_ld_wait();
 #pragma unroll
       for (int j = 0; j < 16; ++j) {
         float2 f = make_float2(0.f, 0.f);
@@ -83,8 +79,16 @@ struct EpiRope {
         v[2 * j] = a * cs - b * sn;
         v[2 * j + 1] = a * sn + b * cs;
       }
-      if (row_ok) store_row32(p.D + static_cast<long long>(c.row) * p.ldd + col, v, ncols);
-    }
+      if (p.use_tma) {
+        const uint32_t tile = ring_acquire(c);
+        stage_row_bf16<32>(tile, c.lane, v);
+        ring_publish();
+        if (c.lane == 0) store_tile(c, &p.tm_d, tile, col);
+        ring_commit(c);
+      } else if (row_ok) {
+        store_row32(p.D + static_cast<long long>(c.row) * p.ldd + col, v, ncols);
+      }
+    });
   }
 };
 
@@ -94,6 +98,8 @@ struct EpiRope {
 // `_gemm_residual_partial_rmsnorm_epi` (coda/core/gemm/functional.py:573-613; epilogues.py:72-80).
 struct EpiResidualNorm {
   struct Params {
+    alignas(64) CUtensorMap tm_pre;   // pre as [M, N], box 32 x 32
+    alignas(64) CUtensorMap tm_post;  // post as [M, N], box 32 x 32
     const __nv_bfloat16* C;  // [M, N] residual (may alias pre or post)
     long long ldc;
     __nv_bfloat16* pre;  // [M, N]
@@ -103,34 +109,46 @@ struct EpiResidualNorm {
     const __nv_bfloat16* weight;  // [N]
     float* part_sq;               // [M, tiles_n]
     int tiles_n;
+    int use_tma;
   };
-  __device__ static void prologue(const Params&, uint8_t*, int) {}
 
   template <int kBN>
-  __device__ static void run(const Params& p, const EpiCtx& c, uint8_t*) {
+  __device__ static void run(const Params& p, EpiCtx& c) {
     const bool row_ok = c.row < c.M;
     const long long r = c.row;
     float sq = 0.f;
-#pragma unroll 1
-    for (int ch = 0; ch < kBN / 32; ++ch) {
+    for_chunks(c.taddr, valid_chunks<kBN>(c.n0, c.N), [&](int ch, float* v) {
       const int col = c.n0 + ch * 32;
-      if (col >= c.N) break;
       const int ncols = c.N - col;
-      float v[32], t[32];
-      tmem_ld32(c.taddr + ch * 32, v);
+      float t[32];
       load_row32(p.C + r * p.ldc + col, t, ncols, row_ok);
-      tmem_ld_wait();
 #pragma unroll
       for (int j = 0; j < 32; ++j) {
         v[j] += t[j];
         if (j < ncols) sq = fmaf(v[j], v[j], sq);
       }
-      if (row_ok) store_row32(p.pre + r * p.ld_pre + col, v, ncols);
+      uint32_t tile = 0;
+      if (p.use_tma) {
+        tile = ring_acquire(c);  // [pre 32 x 64 B | post 32 x 64 B]
+        stage_row_bf16<32>(tile, c.lane, v);
+      } else if (row_ok) {
+        store_row32(p.pre + r * p.ld_pre + col, v, ncols);
+      }
       load_colvec32(p.weight + col, t, ncols);
 #pragma unroll
       for (int j = 0; j < 32; ++j) v[j] *= t[j];
-      if (row_ok) store_row32(p.post + r * p.ld_post + col, v, ncols);
-    }
+      if (p.use_tma) {
+        stage_row_bf16<32>(tile + 2048, c.lane, v);
+        ring_publish();
+        if (c.lane == 0) {
+          store_tile(c, &p.tm_pre, tile, col);
+          store_tile(c, &p.tm_post, tile + 2048, col);
+        }
+        ring_commit(c);
+      } else if (row_ok) {
+        store_row32(p.post + r * p.ld_post + col, v, ncols);
+      }
+    });
     if (row_ok) p.part_sq[r * p.tiles_n + c.tn] = sq;
   }
 };
@@ -141,6 +159,8 @@ struct EpiResidualNorm {
 // `_gemm_swiglu_bwd_zdz_epi(_scaled)` (coda/core/gemm/functional.py:827-910; epilogues.py:105-127).
 struct EpiSwigluBwdZdz {
   struct Params {
+    alignas(64) CUtensorMap tm_dz;    // dZ as [M, 2N], box 32 x 32
+    alignas(64) CUtensorMap tm_post;  // postact as [M, N], box 32 x 32
     const __nv_bfloat16* Z;  // [M, 2N] (may alias dZ)
     long long ldz;
     __nv_bfloat16* dZ;  // [M, 2N]
@@ -149,24 +169,20 @@ struct EpiSwigluBwdZdz {
     long long ld_post;
     float* part_zdz;  // [M, tiles_n]
     int tiles_n;
+    int use_tma;
   };
-  __device__ static void prologue(const Params&, uint8_t*, int) {}
 
   template <int kBN>
-  __device__ static void run(const Params& p, const EpiCtx& c, uint8_t*) {
+  __device__ static void run(const Params& p, EpiCtx& c) {
     const bool row_ok = c.row < c.M;
     const long long r = c.row;
     float zdz = 0.f;
-#pragma unroll 1
-    for (int ch = 0; ch < kBN / 32; ++ch) {
+    for_chunks(c.taddr, valid_chunks<kBN>(c.n0, c.N), [&](int ch, float* t) {
       const int col = c.n0 + ch * 32;  // column of acc / postact; Z and dZ columns are 2*col ..
-      if (col >= c.N) break;
       const int ncols = c.N - col;
-      float t[32], za[32], zb[32];
-      tmem_ld32(c.taddr + ch * 32, t);
+      float za[32], zb[32];
       load_row32(p.Z + r * p.ldz + 2 * col, za, 2 * ncols, row_ok);
       load_row32(p.Z + r * p.ldz + 2 * col + 32, zb, 2 * ncols - 32, row_ok);
-      tmem_ld_wait();
       float out[32];
 #pragma unroll
       for (int j = 0; j < 32; ++j) {
@@ -186,12 +202,27 @@ struct EpiSwigluBwdZdz {
           zb[2 * (j - 16) + 1] = dy;
         }
       }
-      if (row_ok) {
+      if (p.use_tma) {
+        uint32_t tile = ring_acquire(c);  // [dZ first 32 columns | dZ next 32 columns]
+        stage_row_bf16<32>(tile, c.lane, za);
+        stage_row_bf16<32>(tile + 2048, c.lane, zb);
+        ring_publish();
+        if (c.lane == 0) {
+          store_tile(c, &p.tm_dz, tile, 2 * col);
+          if (2 * ncols > 32) store_tile(c, &p.tm_dz, tile + 2048, 2 * col + 32);
+        }
+        ring_commit(c);
+        tile = ring_acquire(c);
+        stage_row_bf16<32>(tile, c.lane, out);
+        ring_publish();
+        if (c.lane == 0) store_tile(c, &p.tm_post, tile, col);
+        ring_commit(c);
+      } else if (row_ok) {
         store_row32(p.dZ + r * p.ld_dz + 2 * col, za, 2 * ncols);
         store_row32(p.dZ + r * p.ld_dz + 2 * col + 32, zb, 2 * ncols - 32);
         store_row32(p.postact + r * p.ld_post + col, out, ncols);
       }
-    }
+    });
     if (row_ok) p.part_zdz[r * p.tiles_n + c.tn] = zdz;
   }
 };
@@ -203,6 +234,8 @@ struct EpiSwigluBwdZdz {
 // `_gemm_residual_partial_rmsnorm_bwd_epi_{store,accum}` (coda/core/gemm/functional.py:655-764; epilogues.py:130-168).
 struct EpiRmsnormBwd {
   struct Params {
+    alignas(64) CUtensorMap tm_dx;      // dX as [M, N], box 32 x 32
+    alignas(64) CUtensorMap tm_normed;  // normed as [M, N], box 32 x 32
     const __nv_bfloat16* pre;  // [M, N]
     long long ld_pre;
     __nv_bfloat16* dX;  // [M, N]
@@ -215,27 +248,23 @@ struct EpiRmsnormBwd {
     const float* alpha;           // device scalar or nullptr
     float* part_dw;               // [ceil(M / 32), N]
     int accumulate;
+    int use_tma;
   };
-  __device__ static void prologue(const Params&, uint8_t*, int) {}
 
   template <int kBN>
-  __device__ static void run(const Params& p, const EpiCtx& c, uint8_t*) {
+  __device__ static void run(const Params& p, EpiCtx& c) {
     const bool row_ok = c.row < c.M;
     const long long r = c.row;
     const float alpha = p.alpha ? __ldg(p.alpha) : 1.0f;
     const float rstd = row_ok ? __ldg(p.rstd + c.row) : 0.f;
     const float zdz = row_ok ? __ldg(p.zdz + c.row) : 0.f;
-    const long long slab = (r - c.lane) / 32;  // the warp's 32 rows start at a multiple of 32
-#pragma unroll 1
-    for (int ch = 0; ch < kBN / 32; ++ch) {
+    const long long slab = c.row0 / 32;  // the warp's 32 rows start at a multiple of 32
+    for_chunks(c.taddr, valid_chunks<kBN>(c.n0, c.N), [&](int ch, float* y) {
       const int col = c.n0 + ch * 32;
-      if (col >= c.N) break;
       const int ncols = c.N - col;
-      float y[32], n[32], w[32];
-      tmem_ld32(c.taddr + ch * 32, y);
+      float n[32], w[32];
       load_row32(p.pre + r * p.ld_pre + col, n, ncols, row_ok);
       load_colvec32(p.weight + col, w, ncols);
-      tmem_ld_wait();
       float d[32];
       if (p.accumulate) load_row32(p.dX + r * p.ld_dx + col, d, ncols, row_ok);
 #pragma unroll
@@ -247,7 +276,17 @@ struct EpiRmsnormBwd {
         w[j] *= n[j];      // normed
         y[j] *= n[j];      // this row's contribution to dweight (zero for rows >= M: acc and pre read as zero)
       }
-      if (row_ok) {
+      if (p.use_tma) {
+        const uint32_t tile = ring_acquire(c);  // [dX 32 x 64 B | normed 32 x 64 B]
+        stage_row_bf16<32>(tile, c.lane, d);
+        stage_row_bf16<32>(tile + 2048, c.lane, w);
+        ring_publish();
+        if (c.lane == 0) {
+          store_tile(c, &p.tm_dx, tile, col);
+          store_tile(c, &p.tm_normed, tile + 2048, col);
+        }
+        ring_commit(c);
+      } else if (row_ok) {
         store_row32(p.dX + r * p.ld_dx + col, d, ncols);
         store_row32(p.normed + r * p.ld_normed + col, w, ncols);
       }
@@ -263,7 +302,7 @@ struct EpiRmsnormBwd {
         }
       }
       if (slab * 32 < c.M && c.lane < ncols) p.part_dw[slab * c.N + col + c.lane] = y[0];
-    }
+    });
   }
 };
 

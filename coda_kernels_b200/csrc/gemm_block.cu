@@ -67,10 +67,13 @@ extern "C" int coda_b200_gemm_residual_partial_rmsnorm(const void* A, int64_t a_
   ep.weight = static_cast<const __nv_bfloat16*>(weight);
   ep.part_sq = part_sq;
   ep.tiles_n = (N + kTileN - 1) / kTileN;
+  int rc = make_tmap_out(&ep.tm_pre, ep.pre, N, M, ld_pre);
+  if (rc == kOk) rc = make_tmap_out(&ep.tm_post, ep.post, N, M, ld_post);
+  if (rc != kOk) return rc;
   Operand a{A, a_stride_m, a_stride_k};
   Operand b{B, b_stride_n, b_stride_k};
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  int rc = launch_gemm<EpiResidualNorm, 3>(a, b, M, N, K, ep, dev_status, st);
+  rc = launch_gemm<EpiResidualNorm, 3>(a, b, M, N, K, ep, dev_status, st);
   if (rc != kOk) return rc;
   row_reduce_kernel<<<(M + 7) / 8, 256, 0, st>>>(part_sq, ep.tiles_n, rstd, M, 1.0f / static_cast<float>(N), eps, 1);
   return launch_check("rstd reduce launch");
@@ -90,6 +93,8 @@ extern "C" int coda_b200_gemm_rmsnorm_rope(const void* A, int64_t a_stride_m, in
   ep.positions = positions;
   ep.pos_is_float = pos_is_float;
   ep.freq = frequencies;
+  const int rc = make_tmap_out(&ep.tm_d, ep.D, N, M, ldd);
+  if (rc != kOk) return rc;
   Operand a{A, a_stride_m, a_stride_k};
   Operand b{B, b_stride_n, b_stride_k};
   return launch_gemm<EpiRope, 0>(a, b, M, N, K, ep, dev_status, static_cast<cudaStream_t>(stream));
@@ -112,10 +117,13 @@ extern "C" int coda_b200_gemm_swiglu_bwd_zdz(const void* A, int64_t a_stride_m, 
   ep.ld_post = ld_post;
   ep.part_zdz = part_zdz;
   ep.tiles_n = (N + kTileN - 1) / kTileN;
+  int rc = make_tmap_out(&ep.tm_dz, ep.dZ, 2LL * N, M, ld_dz);
+  if (rc == kOk) rc = make_tmap_out(&ep.tm_post, ep.postact, N, M, ld_post);
+  if (rc != kOk) return rc;
   Operand a{A, a_stride_m, a_stride_k};
   Operand b{B, b_stride_n, b_stride_k};
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  int rc = launch_gemm<EpiSwigluBwdZdz, 3>(a, b, M, N, K, ep, dev_status, st);
+  rc = launch_gemm<EpiSwigluBwdZdz, 3>(a, b, M, N, K, ep, dev_status, st);
   if (rc != kOk) return rc;
   row_reduce_kernel<<<(M + 7) / 8, 256, 0, st>>>(part_zdz, ep.tiles_n, zdz, M, scale, 0.f, 0);
   return launch_check("zdz reduce launch");
@@ -144,10 +152,13 @@ extern "C" int coda_b200_gemm_residual_partial_rmsnorm_bwd(const void* A, int64_
   ep.alpha = alpha;
   ep.part_dw = part_dw;
   ep.accumulate = accumulate;
+  int rc = make_tmap_out(&ep.tm_dx, ep.dX, N, M, ld_dx);
+  if (rc == kOk) rc = make_tmap_out(&ep.tm_normed, ep.normed, N, M, ld_normed);
+  if (rc != kOk) return rc;
   Operand a{A, a_stride_m, a_stride_k};
   Operand b{B, b_stride_n, b_stride_k};
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  int rc = launch_gemm<EpiRmsnormBwd, 3>(a, b, M, N, K, ep, dev_status, st);
+  rc = launch_gemm<EpiRmsnormBwd, 3>(a, b, M, N, K, ep, dev_status, st);
   if (rc != kOk) return rc;
   const int slabs = (M + 31) / 32;
   col_reduce_kernel<<<(N + 31) / 32, 256, 0, st>>>(part_dw, slabs, N, dW);

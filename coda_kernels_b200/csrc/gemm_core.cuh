@@ -34,19 +34,26 @@ struct GemmShape {
   int tiles_m;  // number of (kBlockM * kCtaGroup)-row tiles
   int tiles_n;  // number of kBN-column tiles
   int group_m;  // raster: tiles of `group_m` consecutive row-tiles share their column sweep (L2 reuse)
-  // Debug overrides for the MN-major descriptor offsets (0 = use the derived values).
-  int dbg_lbo_mn, dbg_sbo_mn;
 };
 
-// Per-thread view of one accumulator tile handed to an epilogue.
+// Per-thread view of one accumulator tile handed to an epilogue.  `ring` and `slot` describe the warp's private
+// staging ring in shared memory: output sub-tiles are written there and leave through TMA stores, so `slot` (and the
+// bulk async-groups still in flight behind it) carries over from one tile to the next.
 struct EpiCtx {
-  int row;         // global row owned by this thread (may be >= M: loads still run, stores are predicated)
+  int row;         // global row owned by this thread (may be >= M: loads still run, stores are clipped / predicated)
+  int row0;        // global row of lane 0 of this warp (the y coordinate of the warp's TMA stores)
   int n0;          // first global column of the tile
   int tn;          // column-tile index
   int M, N;        // problem extents
   uint32_t taddr;  // TMEM address of (this warp's first lane, first column of the accumulator)
   int lane;
+  uint32_t ring;   // shared-memory address of this warp's staging ring (kRingSlots slots of kRingSlotBytes)
+  uint32_t slot;   // slot the next staged sub-tile goes to
 };
+
+constexpr int kRingSlots = 2;
+constexpr uint32_t kRingSlotBytes = 4096;  // 32 rows x 128 bytes: the widest sub-tile an epilogue stages at once
+constexpr uint32_t kRingBytesPerWarp = kRingSlots * kRingSlotBytes;
 
 template <int kCtaGroup, int kBN>
 struct GemmCfg {
@@ -55,12 +62,13 @@ struct GemmCfg {
   static constexpr uint32_t kBBytes = kBNcta * kBlockK * 2;
   static constexpr uint32_t kStageBytes = kABytes + kBBytes;
   static constexpr uint32_t kCtrlBytes = 1024;  // barriers, TMEM pointer, abort word
-  static constexpr uint32_t kEpiScratch = 2048;
+  static constexpr uint32_t kEpiScratch = kNumEpiWarps * kRingBytesPerWarp;  // staging rings of the epilogue warps
   static constexpr int kStagesFit = (kSmemBudget - 1024 - kCtrlBytes - kEpiScratch) / kStageBytes;
   static constexpr int kStages = kStagesFit > 8 ? 8 : kStagesFit;
   static constexpr uint32_t kSmemBytes = 1024 + kStages * kStageBytes + kCtrlBytes + kEpiScratch;
   static constexpr uint32_t kTmemCols = 2 * kBN;  // two accumulator stages
-  static_assert(kBN == 128 || kBN == 256, "tile width must be 128 or 256");
+  static_assert(kBN == 64 || kBN == 128 || kBN == 256, "tile width must be 64, 128 or 256");
+  static_assert((kStages * kStageBytes + kCtrlBytes) % 1024 == 0, "the staging rings must start on a swizzle-atom boundary");
   static_assert(kStages >= 2, "need at least two pipeline stages");
 };
 
@@ -77,7 +85,7 @@ __device__ __forceinline__ void tile_coords(const GemmShape& s, int tile, int& t
 template <int kCtaGroup, int kBN, bool kAMn, bool kBMn, class Epi>
 __global__ void __launch_bounds__(kNumThreads, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b, const GemmShape shape,
-            const typename Epi::Params ep, int* __restrict__ status) {
+            const __grid_constant__ typename Epi::Params ep, int* __restrict__ status) {
   using Cfg = GemmCfg<kCtaGroup, kBN>;
   constexpr int kStages = Cfg::kStages;
   constexpr int kBNcta = Cfg::kBNcta;
@@ -97,7 +105,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
   const uint32_t tmem_slot = bar_acc_empty + 16;         // uint32
   volatile int* abort_word = reinterpret_cast<volatile int*>(smem_gen + kStages * kStageBytes + 16 * kStages + 40);
   volatile uint32_t* tmem_slot_gen = reinterpret_cast<volatile uint32_t*>(smem_gen + kStages * kStageBytes + 16 * kStages + 32);
-  uint8_t* epi_scratch = smem_gen + kStages * kStageBytes + Cfg::kCtrlBytes;
+  const uint32_t epi_rings = ctrl + Cfg::kCtrlBytes;  // 1024-byte aligned: kStageBytes and kCtrlBytes are multiples of 1024
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -127,7 +135,6 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
     tmem_alloc<kCtaGroup>(tmem_slot, Cfg::kTmemCols);
     tmem_relinquish<kCtaGroup>();
   }
-  Epi::prologue(ep, epi_scratch, threadIdx.x);
   tc_fence_before();
   __syncthreads();
   if constexpr (kCtaGroup == 2) {
@@ -199,8 +206,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
     // ============================================================ MMA issuer
     if (leader && lane == 0) {
       constexpr uint32_t idesc = make_idesc_bf16(kBlockM * kCtaGroup, kBN, kAMn, kBMn);
-      const uint32_t lbo_mn = shape.dbg_lbo_mn ? static_cast<uint32_t>(shape.dbg_lbo_mn) : static_cast<uint32_t>(kBlockK * 128);
-      const uint32_t sbo_mn = shape.dbg_sbo_mn ? static_cast<uint32_t>(shape.dbg_sbo_mn) : 1024u;
+      constexpr uint32_t lbo_mn = kBlockK * 128, sbo_mn = 1024u;
       // K-major: 8-row groups 1024 B apart, one MMA step = 32 B along the swizzled row.
       // MN-major: 64-element column blocks kBlockK*128 B apart, 8-k groups 1024 B apart, one MMA step = 2 groups.
       const uint32_t a_lbo = kAMn ? lbo_mn : 16u, a_sbo = kAMn ? sbo_mn : 1024u, a_step = kAMn ? 2048u : 32u;
@@ -249,6 +255,12 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
     // ============================================================ epilogue
     const int q = warp & 3;  // TMEM lane quadrant this warp may read
     const uint32_t acc_empty_sig = (kCtaGroup == 2) ? mapa(bar_acc_empty, 0) : bar_acc_empty;
+    EpiCtx c;
+    c.M = shape.M;
+    c.N = shape.N;
+    c.lane = lane;
+    c.ring = epi_rings + static_cast<uint32_t>(warp - 2) * kRingBytesPerWarp;
+    c.slot = 0;
     uint32_t it = 0;
     for (int tile = cluster_id; tile < num_tiles; tile += num_clusters, ++it) {
       int tm, tn;
@@ -258,15 +270,12 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after();
-      EpiCtx c;
-      c.row = tm * (kBlockM * kCtaGroup) + static_cast<int>(rank) * kBlockM + q * 32 + lane;
+      c.row0 = tm * (kBlockM * kCtaGroup) + static_cast<int>(rank) * kBlockM + q * 32;
+      c.row = c.row0 + lane;
       c.n0 = tn * kBN;
       c.tn = tn;
-      c.M = shape.M;
-      c.N = shape.N;
       c.taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * kBN;
-      c.lane = lane;
-      Epi::template run<kBN>(ep, c, epi_scratch);
+      Epi::template run<kBN>(ep, c);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) {
@@ -274,6 +283,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
         else mbar_arrive(bar_acc_empty + 8 * acc);
       }
     }
+    // Staged sub-tiles still on their way out: the shared memory they are read from and the global writes themselves
+    // must be finished before the CTA exits.
+    if (lane == 0) tma_store_wait_all();
+    __syncwarp();
   }
 
   // ---------------------------------------------------------------- teardown

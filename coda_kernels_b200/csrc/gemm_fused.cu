@@ -27,6 +27,9 @@ int run_gated(const void* A, int64_t a_stride_m, int64_t a_stride_k, const void*
   ep.postact = static_cast<__nv_bfloat16*>(postact);
   ep.ld_post = ld_post;
   ep.row_scale = rstd;
+  int rc = make_tmap_out(&ep.tm_pre, ep.preact, N, M, ld_pre, 32);
+  if (rc == kOk) rc = make_tmap_out(&ep.tm_post, ep.postact, N / 2, M, ld_post, 16);
+  if (rc != kOk) return rc;
   Operand a{A, a_stride_m, a_stride_k};
   Operand b{B, b_stride_n, b_stride_k};
   return launch_gemm<Epi, 0>(a, b, M, N, K, ep, dev_status, static_cast<cudaStream_t>(stream));
@@ -78,9 +81,12 @@ extern "C" int coda_b200_gemm_rmsnorm_lse_zdz(const void* A, int64_t a_stride_m,
     ep.target_logit = target_logit;
     ep.row_scale = rstd;
     ep.part_sz = part_sz;
+    const int rc = make_tmap_out(&ep.tm_p, ep.P, N, M, ldp);
+    if (rc != kOk) return rc;
     return launch_gemm<EpiLse<kLseStoreProbs>, 0>(a, b, M, N, K, ep, dev_status, static_cast<cudaStream_t>(stream));
   }
   EpiLse<kLseStoreNone>::Params ep;
+  memset(&ep.tm_p, 0, sizeof(ep.tm_p));
   ep.P = nullptr;
   ep.ldp = 0;
   ep.part_max = part_max;
@@ -126,6 +132,8 @@ extern "C" int coda_b200_gemm_lse_logits(const void* A, int64_t a_stride_m, int6
   ep.target_logit = nullptr;
   ep.row_scale = rstd;
   ep.part_sz = nullptr;
+  const int rc = make_tmap_out(&ep.tm_p, ep.P, N, M, ld_logits);
+  if (rc != kOk) return rc;
   Operand a{A, a_stride_m, a_stride_k};
   Operand b{B, b_stride_n, b_stride_k};
   return launch_gemm<EpiLse<kLseStoreLogits>, 0>(a, b, M, N, K, ep, dev_status, static_cast<cudaStream_t>(stream));
@@ -152,6 +160,12 @@ int run_qknorm(const Operand& a, const Operand& b, void* qk, int64_t ld_qk, void
   ep.hk = hk;
   ep.eps = eps;
   ep.row_scale = rstd;
+  const long long size_qk = static_cast<long long>(hq + hk) * kHD;
+  int rc = make_tmap_out(&ep.tm_qk, ep.qk, size_qk, M, ld_qk);
+  if (rc == kOk) rc = make_tmap_out(&ep.tm_pre, ep.preact, size_qk, M, ld_pre);
+  if (rc == kOk && N > size_qk) rc = make_tmap_out(&ep.tm_v, ep.v, N - size_qk, M, ld_v);
+  else if (rc == kOk) memset(&ep.tm_v, 0, sizeof(ep.tm_v));
+  if (rc != kOk) return rc;
   return launch_gemm<EpiQKNormRope<kHD>, 0>(a, b, M, N, K, ep, dev_status, static_cast<cudaStream_t>(stream));
 }
 }  // namespace

@@ -3,6 +3,7 @@
 // here allocates device memory or synchronises the device.
 #pragma once
 
+#include <atomic>
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
@@ -27,14 +28,14 @@ inline int fail(int code, const std::string& msg) {
   return code;
 }
 
-// Process-wide tuning / debug options (set through coda_b200_set_option).
+// Process-wide tuning options (set through coda_b200_set_option).  Each field is an atomic, so that a host thread
+// that changes one while another launches never tears a value; a launch reads every option once, at its start.
 struct Options {
-  int cta_group = 2;  // 1 = one CTA per tile (128 rows), 2 = CTA pair per tile (256 rows)
-  int group_m = 0;    // raster group in tiles; 0 = default
-  int max_ctas = 0;   // cap on the persistent grid; 0 = all SMs
-  int tile_n = 0;     // 0 = choose per problem; 128 or 256 forces the column-tile width where both are built
-  int dbg_lbo_mn = 0;
-  int dbg_sbo_mn = 0;
+  std::atomic<int> cta_group{2};  // 1 = one CTA per tile (128 rows), 2 = CTA pair per tile (256 rows)
+  std::atomic<int> group_m{0};    // raster group in tiles; 0 = default
+  std::atomic<int> max_ctas{0};   // cap on the persistent grid; 0 = all SMs
+  std::atomic<int> tile_n{0};     // 0 = choose per problem; 64, 128 or 256 forces the column-tile width where it is built
+  std::atomic<int> epi_tma{1};    // 1 = epilogues stage their output in shared memory and store it with TMA; 0 = per-thread stores
 };
 inline Options& options() {
   static Options o;
@@ -99,21 +100,55 @@ inline int make_tmap_bf16(CUtensorMap* m, const void* ptr, long long inner, long
   return kOk;
 }
 
+// Tensor map of a row-major [rows, cols] output (bf16: elem_bytes 2, fp32: 4) for the staged epilogue stores:
+// box = box_cols columns x 32 rows, swizzled by the box's row width (32, 64 or 128 bytes).
+inline int make_tmap_out(CUtensorMap* m, const void* ptr, int elem_bytes, long long cols, long long rows, long long ld, int box_cols) {
+  EncodeTiledFn fn = encode_tiled_fn();
+  if (!fn) return fail(kNoDriverEntry, "cuTensorMapEncodeTiled not available from the CUDA driver");
+  if ((reinterpret_cast<uintptr_t>(ptr) & 15u) != 0) return fail(kBadArgument, "output base address must be 16-byte aligned");
+  if ((ld * elem_bytes) % 16 != 0 || ld < cols) return fail(kBadArgument, "output leading dimension must cover the row and be a multiple of 16 bytes");
+  const int row_bytes = box_cols * elem_bytes;
+  CUtensorMapSwizzle sw = row_bytes == 128 ? CU_TENSOR_MAP_SWIZZLE_128B : row_bytes == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_32B;
+  if (row_bytes != 128 && row_bytes != 64 && row_bytes != 32) return fail(kBadArgument, "staged sub-tile rows must be 32, 64 or 128 bytes");
+  cuuint64_t dims[2] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows)};
+  cuuint64_t strides[1] = {static_cast<cuuint64_t>(ld * elem_bytes)};
+  cuuint32_t box[2] = {static_cast<cuuint32_t>(box_cols), 32u};
+  cuuint32_t estr[2] = {1u, 1u};
+  CUresult r = fn(m, elem_bytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<void*>(ptr), dims,
+                  strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, sw, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(kCudaError, "cuTensorMapEncodeTiled (output) failed with code " + std::to_string(static_cast<int>(r)));
+  return kOk;
+}
+template <typename T>
+inline int make_tmap_out(CUtensorMap* m, T* ptr, long long cols, long long rows, long long ld, int box_cols = 32) {
+  return make_tmap_out(m, static_cast<const void*>(ptr), static_cast<int>(sizeof(T)), cols, rows, ld, box_cols);
+}
+
 inline int sm_count() {
-  static int cached[64] = {0};
+  static std::atomic<int> cached[64];
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
-  if (cached[dev] == 0) {
-    int n = 0;
+  int n = cached[dev].load(std::memory_order_relaxed);
+  if (n == 0) {
     if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
-    cached[dev] = n;
+    cached[dev].store(n, std::memory_order_relaxed);
   }
-  return cached[dev];
+  return n;
+}
+
+// The options one launch works with, read once.
+struct LaunchOptions {
+  int cta_group, group_m, max_ctas, tile_n, epi_tma;
+};
+inline LaunchOptions launch_options() {
+  const Options& o = options();
+  return LaunchOptions{o.cta_group.load(), o.group_m.load(), o.max_ctas.load(), o.tile_n.load(), o.epi_tma.load()};
 }
 
 template <int kCtaGroup, int kBN, bool kAMn, bool kBMn, class Epi>
 int launch_gemm_cfg(const void* a_ptr, long long lda, const void* b_ptr, long long ldb, int M, int N, int K,
-                    const typename Epi::Params& ep, int* status, cudaStream_t stream) {
+                    const typename Epi::Params& ep, int* status, cudaStream_t stream, const LaunchOptions& opt) {
   using Cfg = GemmCfg<kCtaGroup, kBN>;
   CUtensorMap ta, tb;
   int rc;
@@ -132,25 +167,23 @@ int launch_gemm_cfg(const void* a_ptr, long long lda, const void* b_ptr, long lo
   const int tile_m = kBlockM * kCtaGroup;
   shape.tiles_m = (M + tile_m - 1) / tile_m;
   shape.tiles_n = (N + kBN - 1) / kBN;
-  const Options& opt = options();
   shape.group_m = opt.group_m > 0 ? opt.group_m : (kCtaGroup == 2 ? 8 : 16);
-  shape.dbg_lbo_mn = opt.dbg_lbo_mn;
-  shape.dbg_sbo_mn = opt.dbg_sbo_mn;
   const long long num_tiles = static_cast<long long>(shape.tiles_m) * shape.tiles_n;
   if (num_tiles <= 0 || num_tiles > 0x7fffffffLL) return fail(kBadArgument, "tile count out of range");
 
   auto kern = gemm_kernel<kCtaGroup, kBN, kAMn, kBMn, Epi>;
-  static bool attr_set[64] = {false};
+  // One bit per device: setting the attribute twice is harmless, so two threads racing here only repeat the call.
+  static std::atomic<unsigned long long> attr_set{0ull};
   int dev = 0;
   cudaGetDevice(&dev);
-  if (dev >= 0 && dev < 64 && !attr_set[dev]) {
+  if (dev < 0 || dev >= 64 || ((attr_set.load(std::memory_order_acquire) >> dev) & 1ull) == 0ull) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(Cfg::kSmemBytes));
     if (e != cudaSuccess) return fail(kCudaError, std::string("cudaFuncSetAttribute(smem): ") + cudaGetErrorString(e));
     if (kCtaGroup == 2) {
       e = cudaFuncSetAttribute(kern, cudaFuncAttributeNonPortableClusterSizeAllowed, 0);
       (void)e;
     }
-    attr_set[dev] = true;
+    if (dev >= 0 && dev < 64) attr_set.fetch_or(1ull << dev, std::memory_order_release);
   }
   int sms = sm_count();
   if (opt.max_ctas > 0 && opt.max_ctas < sms) sms = opt.max_ctas;
@@ -178,15 +211,17 @@ int launch_gemm_cfg(const void* a_ptr, long long lda, const void* b_ptr, long lo
   return kOk;
 }
 
-// Column-tile width for epilogues that are built for both 128 and 256 columns.  The narrow tile wins when the
-// wide one would leave the last wave of the persistent grid mostly empty (few output tiles) or when N itself is
-// narrow; otherwise the wide tile is kept, since it reads A once per 256 instead of once per 128 output columns.
-inline int choose_tile_n(int M, int N, int cta_group) {
-  const int forced = options().tile_n;
-  if (forced == 128 || forced == 256) return forced;
+// Column-tile width for epilogues that are built for several widths.  A narrower tile wins when the wide one would
+// leave the last wave of the persistent grid mostly empty (few output tiles) or when N itself is narrow; otherwise
+// the wide tile is kept, since it reads A once per 256 instead of once per 128 output columns.
+inline int choose_tile_n(int M, int N, const LaunchOptions& opt, bool has64) {
+  const int forced = opt.tile_n;
+  if (forced == 128 || forced == 256 || (forced == 64 && has64)) return forced;
+  if (N <= 64 && has64) return 64;  // e.g. one gate per attention head: a streaming kernel, bound by reading A
   if (N <= 128) return 128;
   int sms = sm_count();
-  if (options().max_ctas > 0 && options().max_ctas < sms) sms = options().max_ctas;
+  if (opt.max_ctas > 0 && opt.max_ctas < sms) sms = opt.max_ctas;
+  const int cta_group = opt.cta_group == 2 ? 2 : 1;
   const long long clusters = sms / cta_group > 0 ? sms / cta_group : 1;
   const long long tiles_m = (M + kBlockM * cta_group - 1) / (kBlockM * cta_group);
   const long long w256 = (tiles_m * ((N + 255) / 256) + clusters - 1) / clusters;
@@ -198,9 +233,11 @@ inline int choose_tile_n(int M, int N, int cta_group) {
 }
 
 // Dispatch on CTA grouping, operand majors and (if kNarrow) column-tile width.
-// kAllowMajors: bit0 = allow A MN-major, bit1 = allow B MN-major.
-template <class Epi, int kAllowMajors, bool kNarrow = false>
-int launch_gemm(const Operand& A, const Operand& B, int M, int N, int K, const typename Epi::Params& ep, int* status,
+// kAllowMajors: bit0 = allow A MN-major, bit1 = allow B MN-major.  kNarrow: 0 = 256-column tiles only, 1 = also
+// 128, 2 = also 128 and (for K-major x K-major operands) 64.
+// The caller has encoded the output tensor maps of `ep`; `ep.use_tma` is filled in here from the options.
+template <class Epi, int kAllowMajors, int kNarrow = 0>
+int launch_gemm(const Operand& A, const Operand& B, int M, int N, int K, typename Epi::Params& ep, int* status,
                 cudaStream_t stream) {
   if (M <= 0 || N <= 0 || K <= 0) return fail(kBadArgument, "GEMM extents must be positive");
   if (status == nullptr) return fail(kBadArgument, "device status word is required");
@@ -208,20 +245,27 @@ int launch_gemm(const Operand& A, const Operand& B, int M, int N, int K, const t
   long long lda, ldb;
   if (!classify(A, M, K, &a_mn, &lda)) return fail(kBadLayout, "A must be contiguous along one of its two dimensions");
   if (!classify(B, N, K, &b_mn, &ldb)) return fail(kBadLayout, "B must be contiguous along one of its two dimensions");
-  const bool two = options().cta_group == 2;
-  bool narrow = false;
-  if constexpr (kNarrow) narrow = choose_tile_n(M, N, two ? 2 : 1) == 128;
+  const LaunchOptions opt = launch_options();
+  ep.use_tma = opt.epi_tma;
+  const bool two = opt.cta_group == 2;
+  int tile_n = 256;
+  if constexpr (kNarrow > 0) tile_n = choose_tile_n(M, N, opt, kNarrow == 2 && !a_mn && !b_mn);
 #define CB_LAUNCH_BN(BN, AM, BM)                                                                                   \
-  (two ? launch_gemm_cfg<2, BN, AM, BM, Epi>(A.ptr, lda, B.ptr, ldb, M, N, K, ep, status, stream)                    \
-       : launch_gemm_cfg<1, BN, AM, BM, Epi>(A.ptr, lda, B.ptr, ldb, M, N, K, ep, status, stream))
+  (two ? launch_gemm_cfg<2, BN, AM, BM, Epi>(A.ptr, lda, B.ptr, ldb, M, N, K, ep, status, stream, opt)               \
+       : launch_gemm_cfg<1, BN, AM, BM, Epi>(A.ptr, lda, B.ptr, ldb, M, N, K, ep, status, stream, opt))
 #define CB_LAUNCH(AM, BM)                                                \
   do {                                                                   \
-    if constexpr (kNarrow) {                                             \
-      if (narrow) return CB_LAUNCH_BN(128, AM, BM);                      \
+    if constexpr (kNarrow > 0) {                                         \
+      if (tile_n == 128) return CB_LAUNCH_BN(128, AM, BM);               \
     }                                                                    \
     return CB_LAUNCH_BN(256, AM, BM);                                    \
   } while (0)
-  if (!a_mn && !b_mn) CB_LAUNCH(false, false);
+  if (!a_mn && !b_mn) {
+    if constexpr (kNarrow == 2) {
+      if (tile_n == 64) return CB_LAUNCH_BN(64, false, false);
+    }
+    CB_LAUNCH(false, false);
+  }
   if constexpr ((kAllowMajors & 2) != 0) {
     if (!a_mn && b_mn) CB_LAUNCH(false, true);
   }

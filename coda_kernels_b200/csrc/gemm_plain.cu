@@ -16,16 +16,17 @@ extern "C" int coda_b200_set_option(const char* name, int value) {
     if (value != 1 && value != 2) return fail(kBadArgument, "cta_group must be 1 or 2");
     o.cta_group = value;
   } else if (!strcmp(name, "group_m")) {
+    if (value < 0) return fail(kBadArgument, "group_m must be >= 0");
     o.group_m = value;
   } else if (!strcmp(name, "max_ctas")) {
+    if (value < 0) return fail(kBadArgument, "max_ctas must be >= 0");
     o.max_ctas = value;
   } else if (!strcmp(name, "tile_n")) {
-    if (value != 0 && value != 128 && value != 256) return fail(kBadArgument, "tile_n must be 0, 128 or 256");
+    if (value != 0 && value != 64 && value != 128 && value != 256) return fail(kBadArgument, "tile_n must be 0, 64, 128 or 256");
     o.tile_n = value;
-  } else if (!strcmp(name, "dbg_lbo_mn")) {
-    o.dbg_lbo_mn = value;
-  } else if (!strcmp(name, "dbg_sbo_mn")) {
-    o.dbg_sbo_mn = value;
+  } else if (!strcmp(name, "epi_tma")) {
+    if (value != 0 && value != 1) return fail(kBadArgument, "epi_tma must be 0 or 1");
+    o.epi_tma = value;
   } else {
     return fail(kBadArgument, std::string("unknown option: ") + name);
   }
@@ -34,37 +35,51 @@ extern "C" int coda_b200_set_option(const char* name, int value) {
 
 namespace {
 template <typename OutT, Act kAct>
-int run_store(const void* A, int64_t asm_, int64_t ask, const void* B, int64_t bsk, int64_t bsn, void* D, int64_t ldd, int M,
-              int N, int K, const float* alpha, int* dev_status, void* stream) {
+int run_store(const void* A, int64_t asm_, int64_t ask, const void* B, int64_t bsk, int64_t bsn, const void* C, int64_t ldc,
+              int c_is_fp32, void* D, int64_t ldd, int M, int N, int K, const float* alpha, int* dev_status, void* stream) {
   if (D == nullptr || A == nullptr || B == nullptr) return fail(kBadArgument, "NULL matrix pointer");
   if ((reinterpret_cast<uintptr_t>(D) & 15u) != 0) return fail(kBadArgument, "D must be 16-byte aligned");
   if (N % 8 != 0 || ldd % 8 != 0 || ldd < N) return fail(kBadArgument, "N and ldd must be multiples of 8 with ldd >= N");
+  if (C != nullptr && ((reinterpret_cast<uintptr_t>(C) & 15u) != 0 || ldc % 8 != 0 || ldc < N))
+    return fail(kBadArgument, "C must be 16-byte aligned with ldc a multiple of 8 and >= N");
   typename EpiStore<OutT, kAct>::Params ep;
   ep.D = static_cast<OutT*>(D);
   ep.ldd = ldd;
   ep.alpha = alpha;
+  ep.C = C;
+  ep.ldc = ldc;
+  ep.c_is_fp32 = c_is_fp32;
+  int rc = make_tmap_out(&ep.tm_d, ep.D, N, M, ldd);
+  if (rc != kOk) return rc;
   Operand a{A, asm_, ask};
   Operand b{B, bsn, bsk};
-  return launch_gemm<EpiStore<OutT, kAct>, 3, true>(a, b, M, N, K, ep, dev_status, static_cast<cudaStream_t>(stream));
+  return launch_gemm<EpiStore<OutT, kAct>, 3, 2>(a, b, M, N, K, ep, dev_status, static_cast<cudaStream_t>(stream));
 }
 }  // namespace
+
+extern "C" int coda_b200_gemm_add(const void* A, int64_t a_stride_m, int64_t a_stride_k, const void* B, int64_t b_stride_k,
+                                  int64_t b_stride_n, const void* C, int64_t ldc, int c_is_fp32, void* D, int64_t ldd,
+                                  int d_is_fp32, int M, int N, int K, const float* alpha, int* dev_status, void* stream) {
+  if (d_is_fp32)
+    return run_store<float, Act::kNone>(A, a_stride_m, a_stride_k, B, b_stride_k, b_stride_n, C, ldc, c_is_fp32, D, ldd, M, N, K,
+                                        alpha, dev_status, stream);
+  return run_store<__nv_bfloat16, Act::kNone>(A, a_stride_m, a_stride_k, B, b_stride_k, b_stride_n, C, ldc, c_is_fp32, D, ldd, M, N,
+                                              K, alpha, dev_status, stream);
+}
 
 extern "C" int coda_b200_gemm(const void* A, int64_t a_stride_m, int64_t a_stride_k, const void* B, int64_t b_stride_k,
                               int64_t b_stride_n, void* D, int64_t ldd, int d_is_fp32, int M, int N, int K,
                               const float* alpha, int* dev_status, void* stream) {
-  if (d_is_fp32)
-    return run_store<float, Act::kNone>(A, a_stride_m, a_stride_k, B, b_stride_k, b_stride_n, D, ldd, M, N, K, alpha,
-                                        dev_status, stream);
-  return run_store<__nv_bfloat16, Act::kNone>(A, a_stride_m, a_stride_k, B, b_stride_k, b_stride_n, D, ldd, M, N, K, alpha,
-                                              dev_status, stream);
+  return coda_b200_gemm_add(A, a_stride_m, a_stride_k, B, b_stride_k, b_stride_n, nullptr, 0, 0, D, ldd, d_is_fp32, M, N, K, alpha,
+                            dev_status, stream);
 }
 
 extern "C" int coda_b200_gemm_sigmoid(const void* A, int64_t a_stride_m, int64_t a_stride_k, const void* B,
                                       int64_t b_stride_k, int64_t b_stride_n, void* D, int64_t ldd, int d_is_fp32, int M,
                                       int N, int K, int* dev_status, void* stream) {
   if (d_is_fp32)
-    return run_store<float, Act::kSigmoid>(A, a_stride_m, a_stride_k, B, b_stride_k, b_stride_n, D, ldd, M, N, K, nullptr,
-                                           dev_status, stream);
-  return run_store<__nv_bfloat16, Act::kSigmoid>(A, a_stride_m, a_stride_k, B, b_stride_k, b_stride_n, D, ldd, M, N, K,
-                                                 nullptr, dev_status, stream);
+    return run_store<float, Act::kSigmoid>(A, a_stride_m, a_stride_k, B, b_stride_k, b_stride_n, nullptr, 0, 0, D, ldd, M, N, K,
+                                           nullptr, dev_status, stream);
+  return run_store<__nv_bfloat16, Act::kSigmoid>(A, a_stride_m, a_stride_k, B, b_stride_k, b_stride_n, nullptr, 0, 0, D, ldd, M, N,
+                                                 K, nullptr, dev_status, stream);
 }

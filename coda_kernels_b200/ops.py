@@ -81,12 +81,14 @@ def _noop_fake(*args, **kwargs) -> None:
 
 
 @torch.library.custom_op("coda_b200::gemm_out", mutates_args=("out",), device_types="cuda")
-def _gemm_out(A: Tensor, B: Tensor, out: Tensor, alpha: Optional[Tensor]) -> None:
+def _gemm_out(A: Tensor, B: Tensor, out: Tensor, alpha: Optional[Tensor], C: Optional[Tensor] = None) -> None:
     M, K = A.shape
     N = B.shape[1]
     check(
-        lib.coda_b200_gemm(
-            A.data_ptr(), A.stride(0), A.stride(1), B.data_ptr(), B.stride(0), B.stride(1), out.data_ptr(), out.stride(0),
+        lib.coda_b200_gemm_add(
+            A.data_ptr(), A.stride(0), A.stride(1), B.data_ptr(), B.stride(0), B.stride(1),
+            C.data_ptr() if C is not None else None, C.stride(0) if C is not None else 0,
+            int(C is not None and C.dtype == torch.float32), out.data_ptr(), out.stride(0),
             int(out.dtype == torch.float32), M, N, K, alpha.data_ptr() if alpha is not None else None,
             status_word(A.device).data_ptr(), _stream(A),
         ),
@@ -240,11 +242,12 @@ for _op in (
 
 
 def gemm(A: Tensor, B: Tensor, out: Optional[Tensor] = None, alpha: Optional[Tensor] = None,
-         out_dtype: Optional[torch.dtype] = None) -> Tensor:
-    """``out = alpha * (A @ B)`` for ``A[M,K]``, ``B[K,N]`` (any mix of plain and ``.mT`` views).
+         out_dtype: Optional[torch.dtype] = None, C: Optional[Tensor] = None) -> Tensor:
+    """``out = alpha * (A @ B) + C`` for ``A[M,K]``, ``B[K,N]`` (any mix of plain and ``.mT`` views).
 
     Counterpart of ``gemm`` / ``gemm_scalar_scale`` (coda/core/gemm/functional.py:54-69, 116-132).
-    ``alpha`` is a 0-d or 1-element fp32 device tensor (no host sync).
+    ``alpha`` is a 0-d or 1-element fp32 device tensor (no host sync).  ``C`` (bf16 or fp32, ``[M, N]``, row-major;
+    it may be ``out`` itself) is added to the fp32 accumulator inside the same kernel.
     """
     _require_cuda_bf16(A, B)
     _require(A.dim() == 2 and B.dim() == 2 and A.shape[1] == B.shape[0], "gemm: A[M,K] @ B[K,N] expected")
@@ -254,7 +257,10 @@ def gemm(A: Tensor, B: Tensor, out: Optional[Tensor] = None, alpha: Optional[Ten
     _require(out.dim() == 2 and out.stride(1) == 1 and tuple(out.shape) == (A.shape[0], B.shape[1]), "gemm: bad out")
     if alpha is not None:
         _require(alpha.dtype == torch.float32 and alpha.numel() == 1 and alpha.is_cuda, "gemm: alpha must be a 1-element fp32 CUDA tensor")
-    _gemm_out(A, B, out, alpha)
+    if C is not None:
+        _require(C.is_cuda and C.dtype in (_BF16, torch.float32) and tuple(C.shape) == tuple(out.shape) and C.stride(1) == 1,
+                 "gemm: C must be a row-major bf16 or fp32 CUDA tensor of the output's shape")
+    _gemm_out(A, B, out, alpha, C)
     return out
 
 

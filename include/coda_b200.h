@@ -41,9 +41,13 @@ int coda_b200_version(void);
 /* Message for the last non-zero return code on the calling thread. */
 const char* coda_b200_last_error(void);
 
-/* Tuning / debug switches: "cta_group" (1 or 2), "group_m", "max_ctas",
- * "tile_n" (0 = automatic, 128, 256; plain and sigmoid GEMMs only),
- * "dbg_lbo_mn", "dbg_sbo_mn".  Returns 0, or CODA_B200_EARG for an unknown name. */
+/* Tuning switches: "cta_group" (1 or 2), "group_m", "max_ctas", "tile_n"
+ * (0 = automatic, 64, 128, 256; plain and sigmoid GEMMs only), "epi_tma"
+ * (1 = epilogues stage output tiles in shared memory and write them with TMA
+ * stores, the default; 0 = per-thread 16-byte stores).  Options are
+ * process-wide atomics: a launch reads them once at its start, so changing one
+ * from another host thread is safe and affects later launches only.
+ * Returns 0, or CODA_B200_EARG for an unknown name or value. */
 int coda_b200_set_option(const char* name, int value);
 
 /* Failure-path self-test (no counterpart in the reference).  Launches one warp
@@ -61,7 +65,16 @@ int coda_b200_gemm(const void* A, int64_t a_stride_m, int64_t a_stride_k, const 
                    int64_t b_stride_n, void* D, int64_t ldd, int d_is_fp32, int M, int N, int K, const float* alpha,
                    int* dev_status, void* stream);
 
-/* D = sigmoid(A @ B).  Replaces `coda::_gemm_sigmoid_epi`
+/* D[M,N] = alpha * (A @ B) + C in one kernel: C[M,N] row-major, bf16
+ * (c_is_fp32 = 0) or fp32 (1), leading dimension ldc, may alias D; C = NULL
+ * gives coda_b200_gemm.  Replaces the `C=` form of `gemm`, i.e. quack's
+ * `gemm_add` (coda/core/gemm/functional.py:54-69). */
+int coda_b200_gemm_add(const void* A, int64_t a_stride_m, int64_t a_stride_k, const void* B, int64_t b_stride_k,
+                       int64_t b_stride_n, const void* C, int64_t ldc, int c_is_fp32, void* D, int64_t ldd, int d_is_fp32,
+                       int M, int N, int K, const float* alpha, int* dev_status, void* stream);
+
+/* D = sigmoid(A @ B).  For N <= 64 (one gate per attention head, the shape
+ * the reference benchmarks) a 64-column tile is used.  Replaces `coda::_gemm_sigmoid_epi`
  * (coda/core/gemm/functional.py:199-217; epilogue coda/core/gemm/epilogues.py:39-41). */
 int coda_b200_gemm_sigmoid(const void* A, int64_t a_stride_m, int64_t a_stride_k, const void* B, int64_t b_stride_k,
                            int64_t b_stride_n, void* D, int64_t ldd, int d_is_fp32, int M, int N, int K, int* dev_status,
