@@ -3,11 +3,21 @@
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl b200|reference] [--op NAME]
 
 A step is one forward + backward pass of one operator over one batch of seeded
-synthetic input.  The default workload is ``linear_swiglu`` at the Llama-3-8B
-MLP shape (x [16384, 4096], interleaved weight [28672, 4096]); ``--op`` selects
-the other operators of the path at their benchmark shapes.  With ``--gpus N``
-(one process per GPU under ``torch.distributed.run``) the operator is sharded
-column-, head- or vocab-parallel and the total work stays fixed.
+synthetic input.  The headline workload is ``linear_swiglu`` at the Llama-3-8B
+MLP shape (x [16384, 4096], interleaved weight [28672, 4096]).  Without
+``--op`` the same JSON line also carries an ``ops`` object with the other
+operators of the path (``cross_entropy``, ``qknorm_rope``, ``sigmoid``) at their
+benchmark shapes and, on more than one GPU, ``swiglu_with_dx_allreduce``; with
+``--op NAME`` only that operator is measured, as the headline.  With
+``--gpus N`` (one process per GPU under ``torch.distributed.run``) each operator
+is sharded column-, head- or vocab-parallel and the total work stays fixed.
+
+Timing: W warm-up steps, then windows of exactly K steps, each window bracketed
+by a barrier + synchronize and timed with CUDA events, the maximum over ranks
+taken per window; enough windows are run to cover about a second (at least 5)
+and the MEDIAN window is reported (the per-iteration-median protocol of the
+reference's harness, benchmarks/bench_utils.py:45-82, at window granularity).
+``nvidia-smi`` samples clocks every 20 ms meanwhile.
 
 Rank 0 prints ONE JSON line.  ``value`` is whole-job TFLOP/s (algorithmic GEMM
 flops only) with inputs resident in HBM; ``e2e`` is the same metric with
@@ -15,13 +25,15 @@ host-to-device copies of the inputs and device-to-host copies of the results
 inside the timed region; ``roofline`` describes the dominant kernel (the fused
 forward GEMM) timed alone; ``cpu_baseline`` is the oracle's eager formulation
 timed on the host cores for a bounded row sample.  ``--impl reference`` times
-that CPU formulation alone, as the reference arm.
+that CPU formulation alone, on the same sample, as the reference arm.
 """
 
 from __future__ import annotations
 
 import argparse
+import gc
 import json
+import math
 import os
 import statistics
 import subprocess
@@ -104,7 +116,7 @@ class ClockSampler:
         has to be over before anything is timed."""
         try:
             self.proc = subprocess.Popen(
-                ["nvidia-smi", "-i", str(self.gpu_index), f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100"],
+                ["nvidia-smi", "-i", str(self.gpu_index), f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "20"],
                 stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
         except OSError:
             self.proc = None
@@ -124,10 +136,9 @@ class ClockSampler:
             if len(parts) == 7:
                 self.rows.append(parts)
 
-    def stop(self, first: int = 0, last: int | None = None) -> dict:
-        """Stop sampling; summarise the samples taken between the two marks (the timed region)."""
+    def stop(self) -> None:
         if self.proc is None:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+            return
         self.proc.terminate()
         try:
             self.proc.wait(timeout=5)
@@ -135,6 +146,12 @@ class ClockSampler:
             self.proc.kill()
         if self.thread is not None:
             self.thread.join(timeout=2)
+        self.proc = None
+
+    def summary(self, first: int = 0, last: int | None = None) -> dict | None:
+        """Summarise the samples taken between the two marks (a timed region); sampling goes on."""
+        if self.proc is None and not self.rows:
+            return None
         sm = []
         reasons = set()
         sm_max = None
@@ -211,19 +228,54 @@ class Workload:
             self.kernels_per_step = 18  # 12 GEMMs, 2 rstd + 1 zdz row reductions, 2 dweight column reductions, rope backward
         else:
             raise ValueError(op)
-        self.host = {k: (v.pin_memory() if pinned_host else v) for k, v in host.items()}
         self.dev = {k: v.to(device) for k, v in host.items()}
-        self.h2d_bytes = sum(v.numel() * v.element_size() for v in host.values())
+        # End-to-end leg on several GPUs: the replicated activation `x` is uploaded as one row slice per rank and
+        # all-gathered over NVLink, so the host bytes summed over ranks do not grow with the number of GPUs.
+        self.rows_lo, self.rows_hi = parallel.shard_bounds(s["M"], rank, world, 1)
+        if world > 1 and op != "llama3_block":
+            host["x"] = host["x"][self.rows_lo:self.rows_hi].contiguous()
+        self.host = {k: (v.pin_memory() if pinned_host else v) for k, v in host.items()}
+        self.h2d_bytes = sum(v.numel() * v.element_size() for v in self.host.values())
         self.host_out: dict[str, torch.Tensor] = {}
 
     def upload(self, dst: dict | None = None):
+        """Enqueue the host-to-device copies of one step's inputs on the current stream (plus, on several GPUs, the
+        all-gather that completes `x`)."""
         dst = self.dev if dst is None else dst
         for k, v in self.host.items():
-            dst[k].copy_(v, non_blocking=True)
+            if k == "x" and self.world > 1:
+                dst[k][self.rows_lo:self.rows_hi].copy_(v, non_blocking=True)
+            else:
+                dst[k].copy_(v, non_blocking=True)
+        if self.world > 1:
+            torch.distributed.all_gather_into_tensor(dst["x"], dst["x"][self.rows_lo:self.rows_hi])
 
-    def step(self, dev_inputs: dict | None = None):
-        """Forward + backward through the public operator API.  Returns the result tensors."""
+    def scatter_dx(self, results: dict) -> dict:
+        """On several GPUs: sum the per-rank partial `dx` over ranks, each rank keeping its own row slice."""
+        if self.world == 1 or "dx" not in results:
+            return results
+        dx = results["dx"]
+        mine = torch.empty_like(dx[self.rows_lo:self.rows_hi])
+        torch.distributed.reduce_scatter_tensor(mine, dx)
+        out = dict(results)
+        out["dx"] = mine
+        return out
+
+    def step(self, dev_inputs: dict | None = None, reduce_dx: bool | None = None):
+        """Forward + backward through the public operator API.  Returns the result tensors.
+
+        ``reduce_dx``: all-reduce the input gradient over ranks inside the step.  ``None`` = the operator's own
+        convention: off for the column- and head-parallel operators (each rank keeps its partial sum), on for the
+        vocab-parallel cross entropy (whose wrapper overlaps the all-reduce with the weight-gradient GEMM)."""
         ck, d = self.ck, (self.dev if dev_inputs is None else dev_inputs)
+        if reduce_dx is None:
+            reduce_dx = self.op == "cross_entropy"
+        res = self._step(ck, d, reduce_dx)
+        if reduce_dx and self.world > 1 and self.op != "cross_entropy":
+            self.parallel.allreduce_partial_dx(res["dx"])
+        return res
+
+    def _step(self, ck, d, reduce_dx: bool):
         if self.op == "llama3_block":
             from coda_kernels_b200.blocks import llama3
 
@@ -246,7 +298,8 @@ class Workload:
             if self.world == 1:
                 loss = ck.linear_cross_entropy(x, w, d["target"], -100, "mean")
             else:
-                loss = self.parallel.vocab_parallel_linear_cross_entropy(x, w, d["target"], self.vocab_start, -100, "mean")
+                loss = self.parallel.vocab_parallel_linear_cross_entropy(x, w, d["target"], self.vocab_start, -100, "mean",
+                                                                         reduce_dx=reduce_dx)
             dx, dw = torch.autograd.grad(loss, (x, w))
             return {"loss": loss, "dx": dx, "dweight": dw}
         g = d["gamma"].detach().requires_grad_(True)
@@ -354,20 +407,28 @@ def time_cpu(op: str, rows: int, steps: int, warmup: int) -> tuple[float, float]
     return flops / dt / 1e12, dt
 
 
+CPU_SAMPLE_ROWS = 4096  # one sample size for the in-line cpu_baseline and for the reference arm
+
+
+def cpu_sample_text(op: str, rows: int) -> str:
+    return (f"rows 0..{rows - 1} of {SHAPES[op]['M']} (full K and output width), fwd+bwd, "
+            "oracle eager formulation in fp32 on bf16 inputs")
+
+
 def run_reference_arm(args, rank: int) -> None:
     if rank != 0:
         return
-    s = SHAPES[args.op]
-    rows = args.cpu_rows or 512
-    tflops, dt = time_cpu(args.op, rows, args.steps, max(args.warmup, 1))
+    op = args.op or "swiglu"
+    s = SHAPES[op]
+    rows = args.cpu_rows or CPU_SAMPLE_ROWS
+    tflops, dt = time_cpu(op, rows, args.steps, max(args.warmup, 1))
     cores = torch.get_num_threads()
-    sample = f"rows 0..{rows - 1} of {s['M']} (full K and output width), fwd+bwd, oracle eager formulation in fp32 on bf16 inputs"
     line = {
         "impl": "reference", "metric": METRIC, "value": tflops, "unit": "TFLOP/s", "n_gpus": args.gpus, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
         "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": workload_name(args.op), **s, "parallelism": f"cpu x{cores} threads", "l2": "n/a (host)"},
-        "cpu_baseline": {"value": tflops, "unit": "TFLOP/s", "cores": cores, "kind": "port", "sample": sample},
+        "config": {"workload": workload_name(op), **s, "parallelism": f"cpu x{cores} threads", "l2": "n/a (host)"},
+        "cpu_baseline": {"value": tflops, "unit": "TFLOP/s", "cores": cores, "kind": "port", "sample": cpu_sample_text(op, rows)},
         "e2e": {"value": tflops, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
@@ -385,7 +446,11 @@ def workload_name(op: str) -> str:
     }[op]
 
 
-# ------------------------------------------------------------------------------------------------ main
+PARALLELISM = {"swiglu": "column", "sigmoid": "column", "cross_entropy": "vocab", "qknorm_rope": "head", "llama3_block": "no",
+               "sigmoid_glu": "column"}
+
+
+# ------------------------------------------------------------------------------------------------ result line
 _RESULT_FD = None
 
 
@@ -407,21 +472,247 @@ def emit_result(line: dict) -> None:
         os.write(_RESULT_FD, data)
 
 
+# ------------------------------------------------------------------------------------------------ timing
+class Bench:
+    """What every measurement of one run shares: ranks, the clock sampler, the CUDA graphs to drop before teardown."""
+
+    def __init__(self, args, rank: int, local_rank: int, world: int, device: torch.device):
+        self.args, self.rank, self.local_rank, self.world, self.device = args, rank, local_rank, world, device
+        self.sampler = ClockSampler(local_rank)
+        self.graphs: list = []
+        self.peaks, self.peak_kind = load_peaks()
+        self.peak = float(self.peaks.get("bf16_tflops", FALLBACK_PEAKS["bf16_tflops"]))
+        self.peak_sustained = float(self.peaks.get("bf16_tflops_sustained", FALLBACK_PEAKS["bf16_tflops_sustained"]))
+
+    def barrier(self) -> None:
+        if self.world > 1:
+            torch.distributed.barrier()
+        torch.cuda.synchronize()
+
+    def max_over_ranks(self, ms: float) -> float:
+        if self.world == 1:
+            return ms
+        t = torch.tensor([ms], device=self.device)
+        torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
+        return float(t.item())
+
+    def capture(self, step_fn):
+        """One step (forward, backward, collectives) captured into a CUDA graph: the same public-API calls, minus the
+        per-launch host work.  Returns the replay callable, or None when capture is off or failed."""
+        if self.args.no_graph:
+            return None
+        try:
+            side = torch.cuda.Stream()
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                step_fn()
+            torch.cuda.current_stream().wait_stream(side)
+            torch.cuda.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, capture_error_mode="thread_local"):
+                keep = step_fn()  # the graph's output tensors stay alive with it
+            graph.replay()
+            torch.cuda.synchronize()
+            self.graphs.append((graph, keep))
+            return graph.replay
+        except Exception as ex:  # noqa: BLE001
+            print(f"[bench] CUDA graph capture failed ({type(ex).__name__}: {ex}); timing eager launches", file=sys.stderr)
+            torch.cuda.synchronize()
+            return None
+
+    def drop_graphs(self) -> None:
+        """Destroy every captured graph.  A communicator cannot be torn down while a graph that holds its collectives
+        is alive: that, not NCCL itself, is what blocked destroy_process_group() forever."""
+        while self.graphs:
+            graph, keep = self.graphs.pop()
+            del keep
+            graph.reset()
+            del graph
+        gc.collect()
+        torch.cuda.synchronize()
+
+    def time_windows(self, run_step, steps: int, min_windows: int = 5, target_s: float = 1.0, max_windows: int = 200):
+        """Windows of exactly ``steps`` steps, each bracketed by barrier + synchronize, CUDA events on the launching
+        stream, max over ranks per window.  Returns (median ms per step, per-window ms per step, clock summary)."""
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        per_window: list[float] = []
+        total_ms = 0.0
+        mark0 = self.sampler.mark()
+        while len(per_window) < min_windows or (total_ms < target_s * 1e3 and len(per_window) < max_windows):
+            self.barrier()
+            e0.record()
+            for _ in range(steps):
+                run_step()
+            e1.record()
+            self.barrier()
+            ms = self.max_over_ranks(e0.elapsed_time(e1))
+            per_window.append(ms / steps)
+            total_ms += ms
+        mark1 = self.sampler.mark()
+        clocks = self.sampler.summary(mark0, mark1) if self.rank == 0 else None
+        return statistics.median(per_window), per_window, clocks
+
+
+def measure_device(b: Bench, wl: Workload, reduce_dx: bool | None = None, with_eager: bool = True) -> dict:
+    """Device-resident throughput of one operator: inputs already in HBM when the timed region starts."""
+    args = b.args
+    step_fn = lambda: wl.step(reduce_dx=reduce_dx)  # noqa: E731
+    for _ in range(args.warmup):
+        step_fn()
+    b.barrier()
+    replay = b.capture(step_fn)
+    run_step = replay if replay is not None else step_fn
+    b.barrier()
+    ms_step, windows, clocks = b.time_windows(run_step, args.steps)
+    flops = algorithmic_flops(wl.op, wl.shape)
+    value = flops / (ms_step * 1e-3) / 1e12
+    res = {
+        "value": value, "unit": "TFLOP/s", "ms_per_step": ms_step, "windows": len(windows),
+        "ms_per_step_min": min(windows), "ms_per_step_max": max(windows),
+        "tokens_per_s": wl.shape["M"] / (ms_step * 1e-3),
+        "frac_of_peak": value / (b.world * b.peak), "frac_of_sustained_peak": value / (b.world * b.peak_sustained),
+        "cuda_graph": replay is not None, "clocks": clocks,
+        "ms_x_sm_mhz": (ms_step * clocks["sm_mhz"]) if (clocks and clocks.get("sm_mhz")) else None,
+        "kernels_per_step": wl.kernels_per_step, "gpu_launches": wl.kernels_per_step * args.steps * len(windows),
+    }
+    if with_eager and replay is not None:
+        # the same step with every launch dispatched from Python: what a training loop that does not replay a graph sees
+        ms_eager, w_eager, _ = b.time_windows(step_fn, args.steps, min_windows=3, target_s=0.3)
+        res["value_no_graph"] = flops / (ms_eager * 1e-3) / 1e12
+        res["ms_per_step_no_graph"] = ms_eager
+    return res
+
+
+def measure_e2e(b: Bench, wl: Workload) -> dict:
+    """Host buffers in, host buffers out, every step.  The copies of step i+1 / i-1 run on their own streams while
+    step i computes (double-buffered inputs), as an input pipeline would.  On several GPUs every rank uploads its row
+    slice of `x` (completed by an all-gather) and downloads its row slice of the summed `dx` (reduce-scatter)."""
+    args, world = b.args, b.world
+    compute = torch.cuda.current_stream()
+    up, down = torch.cuda.Stream(), torch.cuda.Stream()
+    bufs = [wl.dev, {k: torch.empty_like(v) for k, v in wl.dev.items()}]
+    ev_up = [torch.cuda.Event(), torch.cuda.Event()]
+    ev_free = [torch.cuda.Event(), torch.cuda.Event()]
+    ev_done = torch.cuda.Event()
+
+    def loop(n):
+        nbytes = 0
+        with torch.cuda.stream(up):
+            wl.upload(bufs[0])
+            ev_up[0].record(up)
+        for i in range(n):
+            k = i % 2
+            if i + 1 < n:
+                with torch.cuda.stream(up):
+                    if i >= 1:
+                        up.wait_event(ev_free[1 - k])
+                    wl.upload(bufs[1 - k])
+                    ev_up[1 - k].record(up)
+            compute.wait_event(ev_up[k])
+            res = wl.scatter_dx(wl.step(bufs[k], reduce_dx=False))
+            ev_free[k].record(compute)
+            ev_done.record(compute)
+            with torch.cuda.stream(down):
+                down.wait_event(ev_done)
+                nbytes = wl.download(res)
+                for t_ in res.values():
+                    t_.record_stream(down)
+        compute.wait_stream(down)
+        compute.wait_stream(up)
+        return nbytes
+
+    loop(3)
+    b.barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    d2h = loop(args.steps)
+    e1.record()
+    b.barrier()
+    ms = b.max_over_ranks(e0.elapsed_time(e1)) / args.steps
+    flops = algorithmic_flops(wl.op, wl.shape)
+    h2d = wl.h2d_bytes
+    if world > 1:  # bytes of the whole job: sum over ranks
+        t = torch.tensor([float(h2d), float(d2h)], device=b.device, dtype=torch.float64)
+        torch.distributed.all_reduce(t)
+        h2d, d2h = int(t[0].item()), int(t[1].item())
+    return {"value": flops / (ms * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": ms, "h2d_bytes_per_step": h2d,
+            "d2h_bytes_per_step": d2h,
+            "bytes_are": "summed over ranks" if world > 1 else "of the one rank",
+            "dx": "reduce-scattered on the device, each rank downloads its row slice" if world > 1 else "downloaded whole"}
+
+
+def measure_kernel(b: Bench, wl: Workload) -> dict:
+    """The dominant kernel (the fused forward GEMM of this rank's shard) launched alone, for the roofline."""
+    label, launch, k_flops = wl.dominant_kernel()
+    for _ in range(3):
+        launch()
+    torch.cuda.synchronize()
+    n_k = max(b.args.steps, 10)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(n_k):
+        launch()
+    e1.record()
+    torch.cuda.synchronize()
+    k_ms = e0.elapsed_time(e1) / n_k
+    achieved = k_flops / (k_ms * 1e-3) / 1e12
+    traffic = NCU_TRAFFIC.get(wl.op) if (b.world == 1 and not b.args.rows) else None
+    return {"bound": "tensor", "kernel": label, "achieved": achieved, "peak": b.peak, "unit": "TFLOP/s", "frac": achieved / b.peak,
+            "peak_kind": f"{b.peak_kind} burst bf16 (kernel timed alone)", "ms_per_launch": k_ms, "flops_per_launch": k_flops,
+            "traffic": traffic}
+
+
+def measure_op(b: Bench, op: str, headline: bool) -> tuple[dict, dict]:
+    """Everything reported for one operator, plus (headline, several GPUs) its variant with the dx all-reduce.  The
+    headline operator also gets the end-to-end leg."""
+    args = b.args
+    wl = Workload(op, b.rank, b.world, b.device, pinned_host=headline and not args.no_e2e, rows=args.rows)
+    res = measure_device(b, wl, with_eager=not args.no_eager)
+    res["workload"] = workload_name(op) + (f" [rows reduced to {args.rows}]" if args.rows else "")
+    res["shape"] = dict(wl.shape)
+    res["parallelism"] = f"{PARALLELISM[op]}-parallel x{b.world}"
+    if b.world > 1:
+        res["dx_reduction"] = ("bf16 all-reduce inside the operator, issued before the weight-gradient GEMM so that the two overlap"
+                               if op == "cross_entropy" else "none: every rank keeps its partial dx (see swiglu_with_dx_allreduce)")
+    else:
+        res["dx_reduction"] = "n/a (one GPU)"
+    extra = {}
+    if headline and b.world > 1 and op != "cross_entropy" and op != "llama3_block":
+        with_ar = measure_device(b, wl, reduce_dx=True, with_eager=False)
+        with_ar["dx_reduction"] = "bf16 all-reduce (NCCL) of the [M, K] input gradient inside every step, after the backward GEMMs"
+        extra[f"{op}_with_dx_allreduce"] = with_ar
+    if headline and not args.no_e2e:
+        res["e2e"] = measure_e2e(b, wl)
+    res["roofline"] = measure_kernel(b, wl)
+    res["l2"] = (f"no flush: every step streams {wl.h2d_bytes / 1e6:.0f} MB of inputs per rank plus larger intermediates, "
+                 "more than the 126 MB L2")
+    from coda_kernels_b200 import ops
+
+    torch.cuda.synchronize()
+    ops.check_device_status(b.device)
+    b.drop_graphs()
+    del wl
+    gc.collect()
+    torch.cuda.empty_cache()
+    return res, extra
+
+
 def main() -> None:
     _claim_stdout()
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--op", default="swiglu", choices=list(SHAPES))
+    ap.add_argument("--op", default=None, choices=list(SHAPES),
+                    help="measure this operator only (as the headline); default: linear_swiglu as the headline plus the other operators under `ops`")
     ap.add_argument("--cpu-rows", type=int, default=0, help="rows of the CPU-baseline sample (0 = default)")
     ap.add_argument("--rows", type=int, default=0, help="override the number of rows M (small captures under ncu); 0 = benchmark shape")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-clocks", action="store_true", help="do not sample nvidia-smi during the timed region")
     ap.add_argument("--no-graph", action="store_true", help="launch every step from Python instead of replaying a CUDA graph of one step")
-    ap.add_argument("--reduce-dx", action="store_true", help="all-reduce the partial dx over ranks inside the step")
+    ap.add_argument("--no-eager", action="store_true", help="skip the extra per-launch-dispatch timing (value_no_graph)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
 
@@ -442,174 +733,57 @@ def main() -> None:
         os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")  # keep NCCL's banner off stdout: rank 0 prints one JSON line there
         torch.distributed.init_process_group("nccl", device_id=device)
 
-    def barrier():
-        if world > 1:
-            torch.distributed.barrier()
-        torch.cuda.synchronize()
-
-    wl = Workload(args.op, rank, world, device, pinned_host=not args.no_e2e, rows=args.rows)
-    from coda_kernels_b200 import ops, parallel
-
-    def full_step():
-        res = wl.step()
-        if args.reduce_dx and world > 1:
-            parallel.allreduce_partial_dx(res["dx"])
-        return res
-
-    # ---- device-resident timing
-    sampler = ClockSampler(local_rank)
+    b = Bench(args, rank, local_rank, world, device)
     if rank == 0 and not args.no_clocks:
-        sampler.start()
-    for _ in range(args.warmup):
-        full_step()
-    barrier()
-    # One step (forward, backward, collectives) captured once and replayed: the same public-API calls, minus the
-    # per-launch host work, which matters once a step is only a millisecond or two of GPU time.
-    graph = None
-    if not args.no_graph:
-        try:
-            side = torch.cuda.Stream()
-            side.wait_stream(torch.cuda.current_stream())
-            with torch.cuda.stream(side):
-                full_step()
-            torch.cuda.current_stream().wait_stream(side)
-            torch.cuda.synchronize()
-            graph = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(graph, capture_error_mode="thread_local"):
-                graph_res = full_step()
-            graph.replay()
-            torch.cuda.synchronize()
-        except Exception as ex:  # noqa: BLE001
-            print(f"[bench] CUDA graph capture failed ({type(ex).__name__}: {ex}); timing eager launches", file=sys.stderr)
-            graph = None
-            torch.cuda.synchronize()
-    run_step = graph.replay if graph is not None else full_step
-    barrier()
-    mark0 = sampler.mark()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for _ in range(args.steps):
-        run_step()
-    e1.record()
-    barrier()
-    mark1 = sampler.mark()
-    ms_total = e0.elapsed_time(e1)
-    clocks = sampler.stop(mark0, mark1) if (rank == 0 and not args.no_clocks) else None
-    ops.check_device_status(device)
-    t = torch.tensor([ms_total], device=device)
-    if world > 1:
-        torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
-    ms_step = float(t.item()) / args.steps
-    flops = algorithmic_flops(args.op, wl.shape)
-    value = flops / (ms_step * 1e-3) / 1e12
+        b.sampler.start()
 
-    # ---- end to end: host buffers in, host buffers out, every step.  The copies of step i+1 / i-1 run on their
-    # own streams while step i computes (double-buffered inputs), as an input pipeline would.
-    e2e = None
-    if not args.no_e2e:
-        compute = torch.cuda.current_stream()
-        up, down = torch.cuda.Stream(), torch.cuda.Stream()
-        bufs = [wl.dev, {k: torch.empty_like(v) for k, v in wl.dev.items()}]
-        ev_up = [torch.cuda.Event(), torch.cuda.Event()]
-        ev_free = [torch.cuda.Event(), torch.cuda.Event()]
-        ev_done = torch.cuda.Event()
-
-        def e2e_loop(n):
-            nbytes = 0
-            with torch.cuda.stream(up):
-                wl.upload(bufs[0])
-                ev_up[0].record(up)
-            for i in range(n):
-                b = i % 2
-                if i + 1 < n:
-                    with torch.cuda.stream(up):
-                        if i >= 1:
-                            up.wait_event(ev_free[1 - b])
-                        wl.upload(bufs[1 - b])
-                        ev_up[1 - b].record(up)
-                compute.wait_event(ev_up[b])
-                res = wl.step(bufs[b])
-                if args.reduce_dx and world > 1:
-                    parallel.allreduce_partial_dx(res["dx"])
-                ev_free[b].record(compute)
-                ev_done.record(compute)
-                with torch.cuda.stream(down):
-                    down.wait_event(ev_done)
-                    nbytes = wl.download(res)
-                    for t_ in res.values():
-                        t_.record_stream(down)
-            compute.wait_stream(down)
-            compute.wait_stream(up)
-            return nbytes
-
-        d2h = e2e_loop(3)
-        barrier()
-        e0.record()
-        d2h = e2e_loop(args.steps)
-        e1.record()
-        barrier()
-        t = torch.tensor([e0.elapsed_time(e1)], device=device)
-        if world > 1:
-            torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
-        e2e_ms = float(t.item()) / args.steps
-        e2e = {"value": flops / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": e2e_ms,
-               "h2d_bytes_per_step": wl.h2d_bytes, "d2h_bytes_per_step": d2h}
-
-    # ---- dominant kernel alone, for the roofline
-    peaks, peak_kind = load_peaks()
-    label, launch, k_flops = wl.dominant_kernel()
-    for _ in range(3):
-        launch()
-    torch.cuda.synchronize()
-    n_k = max(args.steps, 10)
-    e0.record()
-    for _ in range(n_k):
-        launch()
-    e1.record()
-    torch.cuda.synchronize()
-    k_ms = e0.elapsed_time(e1) / n_k
-    achieved = k_flops / (k_ms * 1e-3) / 1e12
-    peak = float(peaks.get("bf16_tflops", FALLBACK_PEAKS["bf16_tflops"]))
-    traffic = NCU_TRAFFIC.get(args.op) if (world == 1 and not args.rows) else None
-    roofline = {"bound": "tensor", "kernel": label, "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
-                "peak_kind": f"{peak_kind} burst bf16 (kernel timed alone)", "ms_per_launch": k_ms, "flops_per_launch": k_flops,
-                "traffic": traffic}
+    head_op = args.op or "swiglu"
+    head, extra = measure_op(b, head_op, headline=True)
+    others = {}
+    if args.op is None:
+        for op in ("cross_entropy", "qknorm_rope", "sigmoid"):
+            others[op], _ = measure_op(b, op, headline=False)
+    others.update(extra)
+    b.sampler.stop()
 
     # ---- CPU baseline (rank 0, single GPU run only)
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
-        rows = args.cpu_rows or 4096
-        tf, dt = time_cpu(args.op, rows, steps=3, warmup=1)
+        rows = args.cpu_rows or CPU_SAMPLE_ROWS
+        tf, dt = time_cpu(head_op, rows, steps=3, warmup=1)
         cpu = {"value": tf, "unit": "TFLOP/s", "cores": torch.get_num_threads(), "kind": "port", "seconds_per_sample_step": dt,
-               "sample": f"rows 0..{rows - 1} of {SHAPES[args.op]['M']} (full K and output width), fwd+bwd, 1 warm-up + 3 timed"}
+               "sample": cpu_sample_text(head_op, rows) + ", 1 warm-up + 3 timed"}
 
     if rank == 0:
-        s = wl.shape
+        s = head["shape"]
         line = {
-            "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
-            "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
+            "metric": METRIC, "value": head["value"], "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": head["ms_per_step"], "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
             "data": "synthetic",
-            "config": {"workload": workload_name(args.op) + (f" [rows reduced to {args.rows}]" if args.rows else ""), **s, "global_batch_tokens": s["M"],
-                       "parallelism": {"swiglu": "column", "sigmoid": "column", "cross_entropy": "vocab", "qknorm_rope": "head", "llama3_block": "no", "sigmoid_glu": "column"}[args.op] + f"-parallel x{world}",
-                       "dx_allreduce": bool(args.reduce_dx and world > 1), "cuda_graph": graph is not None,
-                       "l2": f"no flush: each step streams {wl.h2d_bytes / 1e6:.0f} MB of inputs plus larger intermediates, above the 126 MB L2"},
-            "tokens_per_s": s["M"] / (ms_step * 1e-3),
-            "frac_of_peak": value / (world * peak),
-            "frac_of_sustained_peak": value / (world * float(peaks.get("bf16_tflops_sustained", FALLBACK_PEAKS["bf16_tflops_sustained"]))),
-            "clocks": clocks, "e2e": e2e, "gpu_launches": wl.kernels_per_step * args.steps, "roofline": roofline, "cpu_baseline": cpu,
+            "config": {"workload": head["workload"], **s, "global_batch_tokens": s["M"], "parallelism": head["parallelism"],
+                       "dx_reduction": head["dx_reduction"], "cuda_graph": head["cuda_graph"], "l2": head["l2"],
+                       "timing": f"median of {head['windows']} windows of {args.steps} steps, max over ranks per window"},
+            "tokens_per_s": head["tokens_per_s"], "frac_of_peak": head["frac_of_peak"],
+            "frac_of_sustained_peak": head["frac_of_sustained_peak"],
+            "windows": head["windows"], "ms_per_step_min": head["ms_per_step_min"], "ms_per_step_max": head["ms_per_step_max"],
+            "ms_x_sm_mhz": head["ms_x_sm_mhz"], "value_no_graph": head.get("value_no_graph"),
+            "clocks": head["clocks"], "e2e": head.get("e2e"), "gpu_launches": head["gpu_launches"], "roofline": head["roofline"],
+            "cpu_baseline": cpu, "ops": others,
         }
         emit_result(line)
-    # Leave without tearing NCCL down: destroying a communicator whose collectives were captured in a CUDA graph
-    # blocked ranks forever on this stack, after the result line had been printed.  Everything is synchronised
-    # and flushed first, then every rank exits at once.
-    graph = None
+
+    # ---- teardown: graphs are gone (measure_op dropped them), so the communicator can be destroyed and the
+    # interpreter can exit normally.  The timer only ends a process whose teardown still blocked.
     torch.cuda.synchronize()
+    sys.stderr.flush()
     if world > 1:
+        watchdog = threading.Timer(60.0, lambda: (print("[bench] teardown blocked for 60 s; leaving", file=sys.stderr), os._exit(0)))
+        watchdog.daemon = True
+        watchdog.start()
         torch.distributed.barrier()
         torch.cuda.synchronize()
-    sys.stdout.flush()
-    sys.stderr.flush()
-    os._exit(0)
+        torch.distributed.destroy_process_group()
+        watchdog.cancel()
 
 
 if __name__ == "__main__":

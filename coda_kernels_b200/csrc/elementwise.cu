@@ -242,34 +242,41 @@ __global__ void __launch_bounds__(256) ce_fwd_bwd_kernel(__nv_bfloat16* __restri
 }
 
 // ------------------------------------------------------------------ softmax-gradient fix-up, in place
-// Rows on grid.x (no 65535 limit), 4096 columns per block: each thread owns two 16-byte pieces 2048 columns apart
-// and has both loads in flight before it computes.
+// Rows on grid.x (no 65535 limit), kFixPieces * 2048 columns per block: each thread owns kFixPieces 16-byte pieces
+// 2048 columns apart and has all of their loads in flight before it computes (a pure streaming read-modify-write).
+constexpr int kFixPieces = 4;
 __global__ void __launch_bounds__(256) ce_grad_fixup_kernel(__nv_bfloat16* __restrict__ P, long long ldp,
                                                             const float* __restrict__ part_max, int tiles_n, int tile_w,
                                                             const float* __restrict__ lse, const int* __restrict__ target,
                                                             int ignore_index, int N8) {
   const int row = blockIdx.x;
-  const int c8a = blockIdx.y * 512 + threadIdx.x;
-  const int c8b = c8a + 256;
-  if (c8a >= N8) return;
-  const bool has_b = c8b < N8;
+  const int c8_0 = blockIdx.y * (256 * kFixPieces) + threadIdx.x;
+  if (c8_0 >= N8) return;
   __nv_bfloat16* prow = P + row * ldp;
-  uint4* pa = reinterpret_cast<uint4*>(prow + c8a * 8);
-  uint4* pb = reinterpret_cast<uint4*>(prow + c8b * 8);
   const int tgt = target[row];
   if (tgt == ignore_index) {
-    *pa = make_uint4(0u, 0u, 0u, 0u);
-    if (has_b) *pb = make_uint4(0u, 0u, 0u, 0u);
+#pragma unroll
+    for (int k = 0; k < kFixPieces; ++k) {
+      const int c8 = c8_0 + 256 * k;
+      if (c8 < N8) *reinterpret_cast<uint4*>(prow + c8 * 8) = make_uint4(0u, 0u, 0u, 0u);
+    }
     return;
   }
-  const uint4 va = *pa;
-  const uint4 vb = has_b ? *pb : make_uint4(0u, 0u, 0u, 0u);
+  uint4 v[kFixPieces];
+#pragma unroll
+  for (int k = 0; k < kFixPieces; ++k) {
+    const int c8 = c8_0 + 256 * k;
+    v[k] = (c8 < N8) ? *reinterpret_cast<const uint4*>(prow + c8 * 8) : make_uint4(0u, 0u, 0u, 0u);
+  }
   const float l = lse[row];
   const float* pm = part_max + static_cast<long long>(row) * tiles_n;
-  const float fa = __expf(pm[(c8a * 8) / tile_w] - l);
-  const float fb = has_b ? __expf(pm[(c8b * 8) / tile_w] - l) : 0.f;
-  auto fix = [tgt](const uint4& v, float f, int col) {
-    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+  for (int k = 0; k < kFixPieces; ++k) {
+    const int c8 = c8_0 + 256 * k;
+    if (c8 >= N8) break;
+    const int col = c8 * 8;
+    const float f = __expf(pm[col / tile_w] - l);
+    const uint32_t w[4] = {v[k].x, v[k].y, v[k].z, v[k].w};
     uint32_t r[4];
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
@@ -278,10 +285,8 @@ __global__ void __launch_bounds__(256) ce_grad_fixup_kernel(__nv_bfloat16* __res
       t.y = t.y * f - ((col + 2 * j + 1) == tgt ? 1.0f : 0.0f);
       r[j] = pack_bf16x2(t.x, t.y);
     }
-    return make_uint4(r[0], r[1], r[2], r[3]);
-  };
-  *pa = fix(va, fa, c8a * 8);
-  if (has_b) *pb = fix(vb, fb, c8b * 8);
+    *reinterpret_cast<uint4*>(prow + c8 * 8) = make_uint4(r[0], r[1], r[2], r[3]);
+  }
 }
 
 // ------------------------------------------------------------------ QK-norm + RoPE backward
@@ -578,8 +583,9 @@ extern "C" int coda_b200_ce_grad_fixup(void* P, int64_t ldp, const float* part_m
     return fail(kBadArgument, "P must be 16-byte aligned, N and ldp multiples of 8");
   if (tiles_n != coda_b200_lse_tiles(N)) return fail(kBadArgument, "tiles_n does not match coda_b200_lse_tiles(N)");
   const int N8 = N / 8;
-  if ((N8 + 511) / 512 > 65535) return fail(kBadArgument, "N too large for the fix-up grid");
-  dim3 grid(M, (N8 + 511) / 512, 1);
+  const int per_block = 256 * kFixPieces;
+  if ((N8 + per_block - 1) / per_block > 65535) return fail(kBadArgument, "N too large for the fix-up grid");
+  dim3 grid(M, (N8 + per_block - 1) / per_block, 1);
   ce_grad_fixup_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<__nv_bfloat16*>(P), ldp, part_max,
                                                                            tiles_n, 256, lse, target, ignore_index, N8);
   return launch_check("ce_grad_fixup launch");
@@ -606,6 +612,15 @@ extern "C" int coda_b200_qknorm_rope_bwd(const void* dq, int64_t ld_dq, const vo
   if ((hq > 0 && !aligned16(dq)) || (hk > 0 && !aligned16(dk)) || !aligned16(preact) || !aligned16(grad) || !aligned16(frequencies))
     return fail(kBadArgument, "misaligned pointer");
   if (dv != nullptr && (nv <= 0 || nv % 8 || ld_dv % 8 || !aligned16(dv))) return fail(kBadArgument, "bad dv extent / alignment");
+  if (dv == nullptr && nv > 0) return fail(kBadArgument, "dv is required when nv > 0");
+  // every row must fit inside its leading dimension: the kernel writes and reads rows with 16-byte accesses
+  const long long size_q = static_cast<long long>(hq) * head_dim, size_k = static_cast<long long>(hk) * head_dim;
+  const long long nv_cols = dv ? nv : 0;
+  if (ld_pre < size_q + size_k) return fail(kBadArgument, "ld_pre is smaller than (hq + hk) * head_dim");
+  if (ld_grad < size_q + size_k + nv_cols) return fail(kBadArgument, "ld_grad is smaller than (hq + hk) * head_dim + nv");
+  if (hq > 0 && ld_dq < size_q) return fail(kBadArgument, "ld_dq is smaller than hq * head_dim");
+  if (hk > 0 && ld_dk < size_k) return fail(kBadArgument, "ld_dk is smaller than hk * head_dim");
+  if (dv != nullptr && ld_dv < nv) return fail(kBadArgument, "ld_dv is smaller than nv");
   const int blocks = (M + kQkRowsPerBlock - 1) / kQkRowsPerBlock;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   float* partials = static_cast<float*>(scratch);
@@ -644,20 +659,30 @@ namespace {
 // Device address of g_qk_bwd_scratch on the current device.  In host code the
 // array's name is only a handle for the runtime, never a pointer a kernel may
 // dereference, so the address is looked up once per device and cached.
-int noalloc_scratch_ptr(float** out) {
-  static float* cached[64] = {nullptr};
+int noalloc_scratch_ptr(float** out, const void* caller_buffer) {
+  static std::atomic<float*> cached[64];
   int dev = 0;
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess) return fail(kCudaError, std::string("cudaGetDevice: ") + cudaGetErrorString(e));
   if (dev < 0 || dev >= 64) return fail(kBadArgument, "device ordinal out of range for the built-in scratch table");
-  if (cached[dev] == nullptr) {
+  // The array used is the current device's copy: refuse a call whose buffers live on another GPU rather than run the
+  // kernel against the wrong device's scratch.
+  cudaPointerAttributes attr;
+  const cudaError_t pe = cudaPointerGetAttributes(&attr, caller_buffer);
+  if (pe != cudaSuccess) (void)cudaGetLastError();  // an address the runtime does not know: nothing to compare, clear the error
+  if (pe == cudaSuccess && attr.type == cudaMemoryTypeDevice && attr.device != dev)
+    return fail(kBadArgument, "the buffers of this call live on device " + std::to_string(attr.device) + " but device " +
+                                  std::to_string(dev) + " is current: make the owning device current first");
+  float* ptr = cached[dev].load(std::memory_order_acquire);
+  if (ptr == nullptr) {
     void* p = nullptr;
     e = cudaGetSymbolAddress(&p, g_qk_bwd_scratch);
     if (e != cudaSuccess || p == nullptr)
       return fail(kCudaError, std::string("cudaGetSymbolAddress(g_qk_bwd_scratch): ") + cudaGetErrorString(e));
-    cached[dev] = static_cast<float*>(p);
+    ptr = static_cast<float*>(p);
+    cached[dev].store(ptr, std::memory_order_release);
   }
-  *out = cached[dev];
+  *out = ptr;
   return kOk;
 }
 }  // namespace
@@ -671,8 +696,9 @@ extern "C" int coda_b200_qknorm_rope_bwd_noalloc(const void* dq, int64_t ld_dq, 
     return fail(kBadArgument, "coda_b200_qknorm_rope_bwd_noalloc handles at most " + std::to_string(kNoAllocMaxRows) +
                                   " rows per call (got " + std::to_string(M) + "); split the batch or use coda_b200_qknorm_rope_bwd");
   if (head_dim != 64 && head_dim != 128) return fail(kBadArgument, "head_dim must be 64 or 128");
+  if (grad == nullptr) return fail(kBadArgument, "NULL pointer");
   float* scratch = nullptr;
-  const int rc = noalloc_scratch_ptr(&scratch);
+  const int rc = noalloc_scratch_ptr(&scratch, grad);
   if (rc != kOk) return rc;
   return coda_b200_qknorm_rope_bwd(dq, ld_dq, dk, ld_dk, dv, ld_dv, nv, preact, ld_pre, mean_sq, gamma, positions, pos_is_float,
                                    frequencies, head_dim, hq, hk, eps, grad, ld_grad, dgamma, scratch,

@@ -111,6 +111,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
   const int lane = threadIdx.x & 31;
   const uint32_t rank = (kCtaGroup == 2) ? cluster_ctarank() : 0u;
   const bool leader = (rank == 0);
+  // shared::cluster address of the other CTA's abort word (valid until the cluster barrier of the teardown)
+  const uint32_t peer_abort = (kCtaGroup == 2) ? mapa(ctrl + 16 * kStages + 40, rank ^ 1u) : 0u;
   const int cluster_id = blockIdx.x / kCtaGroup;
   const int num_clusters = gridDim.x / kCtaGroup;
   const int num_tiles = shape.tiles_m * shape.tiles_n;
@@ -200,6 +202,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
           ph ^= 1u;
         }
       }
+      if (!ok) abort_notify_and_drain(peer_abort, *abort_word);
     }
     __syncwarp();
   } else if (warp == 1) {
@@ -249,6 +252,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
         const uint32_t acc = it & 1u, aph = (it >> 1) & 1u;
         ok = mbar_wait(bar_acc_empty + 8 * acc, aph ^ 1u, abort_word, kErrTimeoutAccEmpty);
       }
+      if (!ok) abort_notify_and_drain(peer_abort, *abort_word);
     }
     __syncwarp();
   } else {
@@ -268,7 +272,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
       const uint32_t acc = it & 1u, aph = (it >> 1) & 1u;
       bool ok = mbar_wait(bar_acc_full + 8 * acc, aph, abort_word, kErrTimeoutAccFull);
       ok = __all_sync(0xffffffffu, ok);
-      if (!ok) break;
+      if (!ok) {
+        if (lane == 0) abort_notify_and_drain(peer_abort, *abort_word);
+        __syncwarp();
+        break;
+      }
       tc_fence_after();
       c.row0 = tm * (kBlockM * kCtaGroup) + static_cast<int>(rank) * kBlockM + q * 32;
       c.row = c.row0 + lane;

@@ -122,6 +122,24 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
   return mbar_wait_for(bar, parity, abort_word, code, kWaitTimeoutNs);
 }
 
+// Abort handling of a CTA pair.  A role whose wait expired tells the other CTA of the pair (so that its roles stop at
+// their next poll instead of running into their own time limits one after the other), then lets operations that are
+// already in flight towards this CTA land before it moves on to the teardown: TMA loads into its shared memory and
+// tcgen05.commit arrivals on its barriers complete within microseconds and depend on no other wait, so a fixed grace
+// period covers them.  `peer_abort_addr` is the shared::cluster address of the peer's abort word (0 = no peer);
+// `own_code` is this CTA's abort code: a CTA that only stopped because its peer told it to does not echo the signal,
+// so the code of the wait that really expired survives in the CTA where it happened.
+constexpr unsigned long long kAbortGraceNs = 100000ull;  // 100 us
+__device__ __forceinline__ void abort_notify_and_drain(uint32_t peer_abort_addr, int own_code) {
+  if (peer_abort_addr != 0u && own_code != kErrPeerAbort) {
+    asm volatile("st.relaxed.cluster.shared::cluster.u32 [%0], %1;" ::"r"(peer_abort_addr), "r"(static_cast<uint32_t>(kErrPeerAbort))
+                 : "memory");
+  }
+  const unsigned long long t0 = globaltimer_ns();
+  while (globaltimer_ns() - t0 < kAbortGraceNs) {
+  }
+}
+
 // ---------------------------------------------------------------- TMA
 __device__ __forceinline__ void prefetch_tmap(const CUtensorMap* m) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(m)) : "memory");

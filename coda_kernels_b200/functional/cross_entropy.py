@@ -1,53 +1,42 @@
 """``linear_cross_entropy`` / ``linear_cross_entropy_forward``: LM-head loss without logits in memory.
 
-Same signatures, asserts and autograd behaviour as
-coda/kernels/functional/cross_entropy.py:97-193.  The forward GEMM's epilogue
-keeps an online row max / sum-exp per column tile and stores only unnormalised
-probabilities; one in-place pass turns them into ``softmax - onehot`` (zero for
-ignored rows), which the two backward GEMMs scale by ``dloss / count`` read from
-device memory.  ``fused_lse`` is accepted for signature parity; both values run
-this fused path.
+Drop-in for coda/kernels/functional/cross_entropy.py:97-193 (signatures, defaults, the two asserts, autograd behaviour).
+
+Dataflow here: the forward GEMM's epilogue keeps a row max / sum-exp per column tile and stores only unnormalised
+probabilities; a per-row reduction gives the log-sum-exp and the row losses; one in-place pass turns the stored
+probabilities into ``softmax - onehot`` (exactly zero for ignored rows).  That buffer is the only ``[M, V]`` tensor
+and is what the node saves.  The backward is :func:`linear_backward` over it with ``alpha = dloss / count`` read from
+device memory, so neither direction synchronises with the host.  ``fused_lse`` is accepted for signature parity; both
+values run this path.
 """
 
 import torch
 
 from .._guards import autocast_custom_bwd, autocast_custom_fwd, input_guard
-from ..ops import gemm_lse_dlogits, gemm_lse_select_logits, gemm_scalar_scale
-
-
-def _backward_dlogits(x, weight, dlogits, dloss, need_dx, need_dweight):
-    alpha = dloss.reshape(1).to(dtype=torch.float32)
-    dx = gemm_scalar_scale(dlogits, weight, alpha=alpha) if need_dx else None
-    dweight = gemm_scalar_scale(dlogits.mT, x, alpha=alpha) if need_dweight else None
-    return dx, dweight
+from ..ops import gemm_lse_dlogits, gemm_lse_select_logits
+from ._common import linear_backward, masked_loss
 
 
 class LinearCrossEntropy(torch.autograd.Function):
+    """Saves ``(x, weight, dlogits, inv_count)``; ``dlogits`` is the gradient of the SUM of the row losses."""
+
     @staticmethod
     @input_guard
     @autocast_custom_fwd
     def forward(ctx, x, weight, target, ignore_index: int, reduction: str, fused_lse: bool) -> torch.Tensor:
-        losses, dlogits = gemm_lse_dlogits(x, weight.mT, target, ignore_index)
-        if reduction == "mean":
-            scale = 1.0 / (target != ignore_index).sum().float()
-            loss = losses.sum() * scale
-        else:
-            scale = None
-            loss = losses.sum()
-        ctx.save_for_backward(x, weight, dlogits, scale)
+        row_losses, dlogits = gemm_lse_dlogits(x, weight.mT, target, ignore_index)
+        loss, inv_count = masked_loss(row_losses, target, ignore_index, reduction)
+        ctx.save_for_backward(x, weight, dlogits, inv_count)
         return loss
 
     @staticmethod
     @input_guard
     @autocast_custom_bwd
     def backward(ctx, dloss: torch.Tensor):
-        x, weight, dlogits, scale = ctx.saved_tensors
-        dloss_scaled = dloss * scale if scale is not None else dloss
-        dx, dweight = _backward_dlogits(
-            x=x, weight=weight, dlogits=dlogits, dloss=dloss_scaled,
-            need_dx=ctx.needs_input_grad[0], need_dweight=ctx.needs_input_grad[1],
-        )
-        return dx, dweight, None, None, None, None
+        x, weight, dlogits, inv_count = ctx.saved_tensors
+        alpha = (dloss if inv_count is None else dloss * inv_count).reshape(1).to(dtype=torch.float32)
+        need_dx, need_dw = ctx.needs_input_grad[:2]
+        return (*linear_backward(dlogits, x, weight, need_dx, need_dw, alpha=alpha), None, None, None, None)
 
 
 def linear_cross_entropy(
@@ -63,6 +52,12 @@ def linear_cross_entropy(
     return LinearCrossEntropy.apply(x, weight, target, ignore_index, reduction, fused_lse)
 
 
+@input_guard
+def _forward_only(x, weight, target, ignore_index: int, reduction: str) -> torch.Tensor:
+    row_losses, _, _ = gemm_lse_select_logits(x, weight.mT, target, ignore_index)
+    return masked_loss(row_losses, target, ignore_index, reduction)[0]
+
+
 def linear_cross_entropy_forward(
     x: torch.Tensor,
     weight: torch.Tensor,
@@ -70,10 +65,7 @@ def linear_cross_entropy_forward(
     ignore_index: int = -100,
     reduction: str = "mean",
 ) -> torch.Tensor:
+    """The loss alone: nothing of size ``[M, V]`` is written anywhere."""
     assert reduction in ("mean", "sum")
     assert target.dtype == torch.int32
-    losses, _, _ = gemm_lse_select_logits(x.contiguous(), weight.contiguous().mT, target.contiguous(), ignore_index)
-    if reduction == "mean":
-        scale = 1.0 / (target != ignore_index).sum().float()
-        return losses.sum() * scale
-    return losses.sum()
+    return _forward_only(x, weight, target, ignore_index, reduction)

@@ -43,6 +43,55 @@ def check_device_status(device: Optional[torch.device] = None) -> None:
         raise RuntimeError(f"coda_b200 kernel reported device-side error code {code} (a bounded wait expired)")
 
 
+class _StatusSnapshot:
+    """Pinned host copy of one device's status word plus the event that says when the copy has landed."""
+
+    def __init__(self, device: torch.device):
+        self.host = torch.zeros(1, dtype=torch.int32).pin_memory()
+        self.event = torch.cuda.Event()
+        self.pending = False
+        self.device = device
+
+
+_snapshots: dict[int, _StatusSnapshot] = {}
+
+
+def lazy_status_check(device: Optional[torch.device] = None) -> None:
+    """Report an expired device-side wait without synchronising.
+
+    Called at the start of every operator's forward and backward.  It first looks at the previous snapshot of the
+    status word: if that 4-byte copy has landed (an event query, no wait) and the word is non-zero, it raises.  Then it
+    enqueues a fresh asynchronous copy of the word to pinned host memory on the current stream.  So a kernel that gave
+    up is reported by the next operator call that runs after its launch has finished, typically the backward of the
+    same step, instead of yielding silent garbage for the rest of a training run.  Nothing is done while a CUDA graph
+    is being captured or while ``torch.compile`` traces the caller.
+    """
+    if torch.compiler.is_compiling():
+        return
+    if device is None:
+        device = torch.device("cuda", torch.cuda.current_device())
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    if torch.cuda.is_current_stream_capturing():
+        return
+    snap = _snapshots.get(idx)
+    if snap is None:
+        snap = _snapshots[idx] = _StatusSnapshot(torch.device("cuda", idx))
+    if snap.pending:
+        if not snap.event.query():
+            return  # the previous copy is still behind queued work: look again at the next call
+        snap.pending = False
+        code = int(snap.host[0])
+        if code != 0:
+            status_word(snap.device).zero_()
+            snap.host.zero_()
+            raise RuntimeError(
+                f"coda_b200: a kernel on cuda:{idx} reported device-side error code {code} (a bounded wait expired); "
+                "the outputs of that launch are incomplete")
+    snap.host.copy_(status_word(snap.device), non_blocking=True)
+    snap.event.record()
+    snap.pending = True
+
+
 def _sync_status_hook(what: str) -> None:
     torch.cuda.synchronize()
     for idx, word in list(_status_words.items()):

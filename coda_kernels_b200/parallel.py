@@ -120,6 +120,7 @@ class VocabParallelLinearCrossEntropy(torch.autograd.Function):
     def forward(ctx, x, weight_shard, target, vocab_start: int, ignore_index: int, reduction: str, group, reduce_dx: bool):
         from . import ops
 
+        ops.lazy_status_check(x.device)
         x = x.contiguous()
         weight_shard = weight_shard.contiguous()
         local_target, local_ignore = rebase_target(target, vocab_start, weight_shard.shape[0], ignore_index)
@@ -145,14 +146,19 @@ class VocabParallelLinearCrossEntropy(torch.autograd.Function):
         from . import ops
 
         x, weight_shard, dlogits, scale = ctx.saved_tensors
+        ops.lazy_status_check(x.device)
         alpha = (dloss * scale if scale is not None else dloss).reshape(1).to(dtype=torch.float32)
-        dx = dweight = None
+        dx = dweight = pending = None
         if ctx.needs_input_grad[0]:
             dx = ops.gemm_scalar_scale(dlogits, weight_shard, alpha=alpha)
-            if ctx.reduce_dx:
-                allreduce_partial_dx(dx, ctx.group)
+            if ctx.reduce_dx and dist.is_initialized() and dist.get_world_size(ctx.group) > 1:
+                # asynchronous: the all-reduce runs on the communicator's stream while the weight-gradient GEMM
+                # below runs on this one; the streams are joined only after that GEMM has been enqueued
+                pending = dist.all_reduce(dx, op=dist.ReduceOp.SUM, group=ctx.group, async_op=True)
         if ctx.needs_input_grad[1]:
             dweight = ops.gemm_scalar_scale(dlogits.mT, x, alpha=alpha)
+        if pending is not None:
+            pending.wait()
         return dx, dweight, None, None, None, None, None, None
 
 

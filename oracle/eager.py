@@ -307,3 +307,21 @@ def rel_l2_err(a: torch.Tensor, b: torch.Tensor) -> float:
     denom = b.norm().item()
     num = (a - b).norm().item()
     return float(num) if denom == 0.0 else float(num / denom)
+
+
+def rounding_floor(b: torch.Tensor, dtype: torch.dtype) -> float:
+    """Relative L2 error of the exact answer ``b`` once rounded to ``dtype``: the least error any implementation that
+    returns ``dtype`` can have (the reference's ``errors_minimum``, benchmarks/utils/numerics.py:81-85)."""
+    b64 = b.detach().to(dtype=torch.float64)
+    return rel_l2_err(b64.to(dtype=dtype), b64)
+
+
+def max_elementwise_err(a: torch.Tensor, b: torch.Tensor, atol_frac: float = 1e-6) -> float:
+    """``max |a - b| / (|b| + atol)`` with ``atol = atol_frac * max|b|``: an element-wise relative error with an absolute
+    floor, which sees a wrong small-magnitude entry that ``max_rel_err`` (one global scale) cannot."""
+    a = a.detach().to(device=b.device, dtype=torch.float64)
+    b = b.detach().to(dtype=torch.float64)
+    atol = atol_frac * b.abs().max().item()
+    if atol == 0.0:
+        return float((a - b).abs().max().item())
+    return float(((a - b).abs() / (b.abs() + atol)).max().item())

@@ -51,6 +51,43 @@ def test_host_side_argument_checks_need_no_gpu():
         _lib.check(-1, "probe")
 
 
+def test_qknorm_rope_bwd_rejects_rows_that_do_not_fit_their_leading_dimension():
+    """The backward kernel reads and writes whole rows with 16-byte accesses: a leading dimension shorter than the row
+    is refused on the host (fake, aligned, never dereferenced addresses: no GPU needed)."""
+    from coda_kernels_b200 import _lib
+
+    lib = _lib.lib
+    p = 1 << 20  # 16-byte aligned stand-in for every device pointer
+    hq, hk, d, nv, M = 4, 2, 128, 256, 64
+    size_qk = (hq + hk) * d
+
+    def call(ld_dq=hq * d, ld_dk=hk * d, ld_dv=nv, ld_pre=size_qk, ld_grad=size_qk + nv, dv=p, nv_=nv, scratch_bytes=1 << 20):
+        return lib.coda_b200_qknorm_rope_bwd(p, ld_dq, p, ld_dk, dv, ld_dv, nv_, p, ld_pre, p, p, p, 0, p, d, hq, hk, 1e-6, p, ld_grad,
+                                             p, p, scratch_bytes, M, None)
+
+    for kwargs, text in (
+        ({"ld_grad": size_qk + nv - 8}, b"ld_grad"),
+        ({"ld_pre": size_qk - 8}, b"ld_pre"),
+        ({"ld_dq": hq * d - 8}, b"ld_dq"),
+        ({"ld_dk": hk * d - 8}, b"ld_dk"),
+        ({"ld_dv": nv - 8}, b"ld_dv"),
+        ({"dv": None}, b"dv is required"),
+    ):
+        assert call(**kwargs) == -1, kwargs
+        assert text in lib.coda_b200_last_error(), (kwargs, lib.coda_b200_last_error())
+    assert call(scratch_bytes=0) == -1 and b"scratch" in lib.coda_b200_last_error()
+
+
+def test_options_accept_only_documented_values():
+    from coda_kernels_b200 import _lib
+
+    lib = _lib.lib
+    for name, bad, good in ((b"tile_n", 96, 0), (b"epi_tma", 2, 1), (b"group_m", -1, 0), (b"max_ctas", -5, 0)):
+        assert lib.coda_b200_set_option(name, bad) == -1
+        assert lib.coda_b200_set_option(name, good) == 0
+    assert lib.coda_b200_set_option(b"dbg_lbo_mn", 1) == -1, "bring-up knobs are gone from the ABI"
+
+
 def test_ops_refuse_cpu_tensors():
     import torch
 

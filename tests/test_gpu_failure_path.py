@@ -37,3 +37,34 @@ def test_bounded_wait_expires_and_reports():
     # bad arguments are refused on the host
     assert _lib.lib.coda_b200_selftest_wait_timeout(None, 10, None, None) == -1
     assert _lib.lib.coda_b200_selftest_wait_timeout(word.data_ptr(), 0, None, None) == -1
+
+
+def test_operator_path_reports_an_expired_wait_without_sync():
+    """A kernel that gave up is reported by a later operator call on its own (no explicit status read, no
+    CODA_B200_SYNC_STATUS): the guards look at an asynchronous snapshot of the status word."""
+    import coda_kernels_b200 as ck
+    from coda_kernels_b200 import _lib, ops
+
+    dev = torch.device(DEV)
+    word = ops.status_word(dev)
+    torch.cuda.synchronize()
+    ops.check_device_status(dev)  # start clean
+    x = torch.randn(256, 128, device=dev).to(torch.bfloat16).requires_grad_(True)
+    w = torch.randn(256, 128, device=dev).to(torch.bfloat16).requires_grad_(True)
+    ck.linear_swiglu(x, w).sum().backward()  # healthy step: nothing is raised, snapshots read zero
+    torch.cuda.synchronize()
+    rc = _lib.lib.coda_b200_selftest_wait_timeout(word.data_ptr(), 2000, None, torch.cuda.current_stream().cuda_stream)
+    assert rc == 0
+    with pytest.raises(RuntimeError, match="device-side error code"):
+        for _ in range(4):  # forward snapshots the word, a later call finds the snapshot non-zero
+            out = ck.linear_swiglu(x, w)
+            torch.cuda.synchronize()
+            out.sum().backward()
+            torch.cuda.synchronize()
+    # the report cleared the word; the next steps run normally
+    torch.cuda.synchronize()
+    ck.linear_swiglu(x, w).sum().backward()
+    torch.cuda.synchronize()
+    ck.linear_swiglu(x, w).sum().backward()
+    torch.cuda.synchronize()
+    ops.check_device_status(dev)

@@ -1,8 +1,13 @@
 """Parity of the CUDA operators (called through the public API, i.e. through the C ABI) with the oracle.
 
 Tolerances are the ones the task states: bf16 outputs and gradients
-``max|a-b| / max|b| <= 2e-2``, loss relative error ``<= 1e-3``, ignore-index
-masking and label indexing bit-exact.
+``max|a-b| / max|b| <= 2e-2`` (a normalised max-abs error), loss relative error
+``<= 1e-3``, ignore-index masking and label indexing bit-exact.  On top of
+that every bf16 tensor is held to the reference harness's own metric: its
+relative L2 error against the oracle must stay within ``L2_FACTOR`` times the
+rounding floor (the error of the oracle itself once rounded to bf16,
+benchmarks/utils/numerics.py:20-29, 81-85); gradients that pass through one
+more bf16 tensor (the saved pre-activation gradient) get ``L2_FACTOR_GRAD``.
 """
 
 import functools
@@ -16,6 +21,8 @@ pytestmark = pytest.mark.gpu
 
 TOL = 2e-2
 LOSS_TOL = 1e-3
+L2_FACTOR = 2.0       # outputs computed from the fp32 accumulator
+L2_FACTOR_GRAD = 3.0  # gradients formed from a bf16-rounded intermediate (dx, dweight, dgamma)
 DEV = "cuda:0"
 
 
@@ -33,7 +40,12 @@ def load(golden_dir, name):
 
 def close(a, b, tol=TOL, what=""):
     err = eager.max_rel_err(a, b)
-    assert err <= tol, f"{what}: max rel err {err:.3e} > {tol:.1e} (rel L2 {eager.rel_l2_err(a, b):.3e})"
+    l2 = eager.rel_l2_err(a, b)
+    assert err <= tol, f"{what}: max rel err {err:.3e} > {tol:.1e} (rel L2 {l2:.3e})"
+    if a.dtype == torch.bfloat16:
+        floor = eager.rounding_floor(b, torch.bfloat16)
+        factor = L2_FACTOR_GRAD if what.startswith("d") else L2_FACTOR
+        assert l2 <= factor * floor + 1e-6, f"{what}: rel L2 {l2:.3e} > {factor} x the bf16 rounding floor {floor:.3e}"
     return err
 
 
@@ -158,6 +170,9 @@ def test_cross_entropy_golden(ck, golden_dir, name):
     status_ok(ck)
     close(losses, g["row_losses"], tol=LOSS_TOL, what="row losses")
     close(dlogits, g["dlogits"], what="dlogits")
+    # element-wise: tiny softmax entries pass two bf16 roundings (the stored probability, then the rescaled gradient)
+    ew = eager.max_elementwise_err(dlogits, g["dlogits"])
+    assert ew <= 2e-2, f"dlogits: element-wise relative error {ew:.3e}"
     ignored = (d["target"] == -100).to(DEV)
     assert ignored.any()
     assert (losses[ignored] == 0).all(), "ignored rows must have exactly zero loss"
@@ -165,6 +180,21 @@ def test_cross_entropy_golden(ck, golden_dir, name):
     valid = ~ignored
     assert torch.equal(dlogits[valid].float().argmin(dim=1).int(), d["target"].to(DEV)[valid]), "the one negative entry of a row sits at its label"
     assert (dlogits[valid].float().min(dim=1).values < 0).all()
+
+
+def test_cross_entropy_second_call_and_inputs_untouched(ck):
+    """The gradient buffer is rewritten in place inside the forward; a second step on the same inputs must give the same
+    bits, and the inputs must come out unchanged (the reference harness reads the second call for this reason,
+    benchmarks/utils/numerics.py:48-57)."""
+    d = inputs.cross_entropy_inputs(520, 264, 1544, seed=9, ignore_frac=0.1)
+    x0, w0 = d["x"].to(DEV), d["weight"].to(DEV)
+    xc, wc = x0.clone(), w0.clone()
+    first = run_ce(ck, {"x": x0, "weight": w0, "target": d["target"]}, "mean")
+    second = run_ce(ck, {"x": x0, "weight": w0, "target": d["target"]}, "mean")
+    status_ok(ck)
+    assert torch.equal(x0, xc) and torch.equal(w0, wc), "inputs were clobbered"
+    for a, b, n in zip(first, second, ("loss", "dx", "dweight")):
+        assert torch.equal(a, b), f"{n} differs between two calls on the same inputs"
 
 
 @pytest.mark.parametrize("reduction", ["mean", "sum"])
@@ -223,6 +253,8 @@ def test_qknorm_rope_golden(ck, golden_dir, name):
     close(dx, g["dx"], what="dx")
     close(dw, g["dweight"], what="dweight")
     close(dg, g["dgamma"], what="dgamma")
+    ew = eager.max_elementwise_err(dg, g["dgamma"], atol_frac=1e-3)
+    assert ew <= 2e-2, f"dgamma: element-wise relative error {ew:.3e}"
     assert dg.dtype == torch.bfloat16
 
 
@@ -385,3 +417,76 @@ def test_sigmoid_glu_vs_oracle(ck, shape):
     close(out, ro, what="out")
     close(dx, g["x"], what="dx")
     close(dw, g["weight"], what="dweight")
+
+
+# ------------------------------------------------------------------------------------------------ epilogue store paths, fused addend, 64-column tile
+@pytest.mark.parametrize("epi_tma", [0, 1])
+def test_store_paths_agree_bitwise(ck, epi_tma):
+    """Staged TMA stores and per-thread stores write the same bits, on ragged shapes where the hardware clips the boxes."""
+    d = inputs.swiglu_inputs(333, 264, 136)
+    dq = inputs.qknorm_rope_inputs(300, 256, 128, 4, 1, 1, seq_len=512)
+    dc = inputs.cross_entropy_inputs(300, 256, 1000, ignore_frac=0.1)
+    cfg = {"head_dim": 128, "hq": 4, "hk": 1, "eps": 1e-6}
+
+    def run_all():
+        a = run_swiglu(ck, d)
+        (q, k, v), gq = run_qk(ck, dq, cfg)
+        c = run_ce(ck, dc, "mean")
+        s32 = ck.linear_sigmoid(d["x"].to(DEV), d["weight"].to(DEV), torch.float32)
+        status_ok(ck)
+        return [*a, q, k, v, *gq, *c, s32]
+
+    ck.set_option("epi_tma", epi_tma)
+    try:
+        got = run_all()
+    finally:
+        ck.set_option("epi_tma", 1)
+    ref = run_all()
+    for i, (a, b) in enumerate(zip(got, ref)):
+        assert torch.equal(a, b), f"output {i} differs between epi_tma={epi_tma} and the default"
+
+
+@pytest.mark.parametrize("c_dtype,out_dtype", [(torch.bfloat16, torch.bfloat16), (torch.float32, torch.bfloat16), (torch.float32, torch.float32)])
+def test_gemm_with_addend_is_one_kernel(ck, c_dtype, out_dtype):
+    """``gemm(A, B, C=...)``: the addend joins the fp32 accumulator in the epilogue (the reference's ``quack_gemm_add`` form,
+    coda/core/gemm/functional.py:54-69), also in place (``out is C``) and through the reference-shaped shim."""
+    from coda.core.gemm.functional import gemm as shim_gemm
+
+    gen = torch.Generator().manual_seed(21)
+    M, K, N = 392, 264, 520
+    A = torch.randn(M, K, generator=gen).to(torch.bfloat16).to(DEV)
+    W = torch.randn(N, K, generator=gen).to(torch.bfloat16).to(DEV)
+    C = torch.randn(M, N, generator=gen).to(c_dtype).to(DEV)
+    ref = A.float() @ W.float().mT + C.float()
+    out = ck.ops.gemm(A, W.mT, C=C, out_dtype=out_dtype)
+    status_ok(ck)
+    assert out.dtype == out_dtype
+    close(out, ref, tol=TOL if out_dtype == torch.bfloat16 else 1e-5, what="A @ B + C")
+    if c_dtype == out_dtype:
+        buf = C.clone()
+        ck.ops.gemm(A, W.mT, out=buf, C=buf)
+        status_ok(ck)
+        assert torch.equal(buf, out), "accumulating in place must give the same bits"
+    if out_dtype == torch.bfloat16:
+        assert torch.equal(shim_gemm(A, W.mT, C=C), out)
+
+
+@pytest.mark.parametrize("cta_group", [1, 2])
+@pytest.mark.parametrize("n_gates", [8, 32, 64])
+def test_skinny_sigmoid_uses_the_64_column_tile(ck, n_gates, cta_group):
+    """``linear_sigmoid`` with one gate per attention head (the shape the reference benchmarks, benchmarks/linear.py:28-42)."""
+    d = inputs.sigmoid_inputs(1000, 520, n_gates)
+    ck.set_option("cta_group", cta_group)
+    try:
+        x, w = leaf(d["x"]), leaf(d["weight"])
+        out = ck.linear_sigmoid(x, w)
+        dx, dw = torch.autograd.grad(out, (x, w), d["dout"].to(DEV))
+        out32 = ck.linear_sigmoid(d["x"].to(DEV), d["weight"].to(DEV), torch.float32)
+        status_ok(ck)
+    finally:
+        ck.set_option("cta_group", 2)
+    (ro,), grads = eager.fwd_bwd(eager.linear_sigmoid, {"x": d["x"].to(DEV), "weight": d["weight"].to(DEV)}, ["x", "weight"], d["dout"].to(DEV))
+    close(out, ro, what="out")
+    close(out32, ro, tol=1e-4, what="out fp32")
+    close(dx, grads["x"], what="dx")
+    close(dw, grads["weight"], what="dweight")
