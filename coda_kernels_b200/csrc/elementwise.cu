@@ -290,144 +290,283 @@ __global__ void __launch_bounds__(256) ce_grad_fixup_kernel(__nv_bfloat16* __res
 }
 
 // ------------------------------------------------------------------ QK-norm + RoPE backward
-constexpr int kQkRowsPerBlock = 16;
+constexpr int kQkRowsPerBlock = 16;  // unit of the dgamma workspace: one partial row per 16 input rows at most
 constexpr int kQkWarps = 8;
+constexpr int kQkBlocksPerSm = 3;  // what the kernel's register and shared-memory budget allows to be resident
 
-// A group of kHD/8 lanes owns one (row, head): each lane handles 8 consecutive elements (16-byte accesses), so a
-// warp works on 2 (kHD = 128) or 4 (kHD = 64) heads of a row at once.  Per head: un-rotate dy, take the RMSNorm
-// VJP at the saved statistic, accumulate the gamma gradient in registers; at the end the block folds its warps
-// and writes one partial row of [gamma_q | gamma_k] sums.
+// A group of kHD/8 lanes owns one ROW and walks over a run of its heads: each lane handles the same 8 consecutive
+// elements (16-byte accesses) of every head, so a warp works on 2 (kHD = 128) or 4 (kHD = 64) rows at once and reads
+// their heads as contiguous streams.  Work items are (row group, run of kQkHeadsPerItem heads), handed out to the
+// warps of a persistent grid in order, which keeps every SM busy to the end.
+//
+// Memory pipeline: every thread streams its own (dy, preact, mean_sq) pieces through a private ring of kQkDepth
+// slots in shared memory with cp.async, one commit group per (item, head), so kQkDepth heads are in flight per
+// thread without holding registers: an HBM-bound pass needs tens of kilobytes in flight per SM, more than a
+// register-resident prefetch can hold at this kernel's register count.
+//
+// The rotation angle depends on (row, element) and on the head's frequencies only: as long as a head carries the
+// same frequencies as the one before it (the layout make_rope_frequencies produces), its sines and cosines are
+// reused.  Per head: un-rotate dy, take the RMSNorm VJP at the saved statistic, accumulate the gamma gradient in
+// registers; at the end the block folds its warps and writes one partial row of [gamma_q | gamma_k] sums.
+constexpr int kQkHeadsPerItem = 8;
+constexpr int kQkDepth = 6;
+constexpr int kQkThreads = kQkWarps * 32;
+constexpr int kQkRingBytes = kQkDepth * kQkThreads * (16 + 16 + 4);  // dy piece, preact piece, mean_sq per slot and thread
+
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async4(uint32_t dst, const void* src) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int kPending>
+__device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;" ::"n"(kPending) : "memory");
+}
+
 template <int kHD>
-__global__ void __launch_bounds__(kQkWarps * 32)
+__global__ void __launch_bounds__(kQkThreads, kQkBlocksPerSm)
 qknorm_rope_bwd_kernel(const __nv_bfloat16* __restrict__ dq, long long ld_dq, const __nv_bfloat16* __restrict__ dk,
                        long long ld_dk, const __nv_bfloat16* __restrict__ dv, long long ld_dv, int nv8,
                        const __nv_bfloat16* __restrict__ preact, long long ld_pre, const float* __restrict__ mean_sq,
                        const __nv_bfloat16* __restrict__ gamma, const void* __restrict__ positions, int pos_is_float,
                        const float* __restrict__ freq, int hq, int hk, float eps, __nv_bfloat16* __restrict__ grad,
                        long long ld_grad, float* __restrict__ partials, int M) {
-  constexpr int kG = kHD / 8;     // lanes per head
-  constexpr int kHPW = 32 / kG;   // heads per warp iteration
+  constexpr int kG = kHD / 8;    // lanes per row
+  constexpr int kRPW = 32 / kG;  // rows per warp
   constexpr float kTwoPi = 6.283185307179586f;
-  __shared__ float red[kQkWarps * kHPW][2 * kHD];
-  __shared__ float gam_s[2 * kHD];
+  extern __shared__ __align__(16) uint8_t qk_smem[];
+  float(*red)[2 * kHD] = reinterpret_cast<float(*)[2 * kHD]>(qk_smem + kQkRingBytes);  // [kQkWarps * kRPW][2 * kHD]
+  const uint32_t ring = smem_u32(qk_smem);
+  // slot i of this thread: dy piece at ring_a + i * stride16, preact piece at ring_b + ..., mean_sq at ring_m + ...
+  const uint32_t ring_a = ring + threadIdx.x * 16;
+  const uint32_t ring_b = ring + kQkDepth * kQkThreads * 16 + threadIdx.x * 16;
+  const uint32_t ring_m = ring + 2 * kQkDepth * kQkThreads * 16 + threadIdx.x * 4;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int sub = lane % kG, grp = lane / kG;
   const int heads = hq + hk;
-  const int row0 = blockIdx.x * kQkRowsPerBlock;
-  const int nrows = min(kQkRowsPerBlock, M - row0);
   const int e0 = sub * 8;
-  for (int c = threadIdx.x; c < 2 * kHD; c += blockDim.x) gam_s[c] = __bfloat162float(gamma[c]);
-  __syncthreads();
+  // the lanes of one row reduce among themselves only: rows of a warp may be past the end independently
+  const unsigned group_mask = (kG == 32 ? 0xffffffffu : ((1u << kG) - 1u)) << (grp * kG);
 
-  float gq[8], gk[8];
+  // Do all heads carry the frequencies of head 0 (the layout make_rope_frequencies produces)?  Checked once per
+  // block; if so the sines and cosines of a row are computed once per work item instead of once per head.
+  int same_here = 1;
+  for (int i = threadIdx.x; i < heads * kHD; i += blockDim.x) same_here &= (freq[i] == freq[i % kHD]) ? 1 : 0;
+  const bool periodic = __syncthreads_and(same_here) != 0;
+
+  // gamma as fp32 in shared memory, read once per work item (its 8-float pieces sit 32 bytes apart from lane to lane,
+  // a bank conflict that would hurt inside the head loop but not once per item); the per-lane dgamma sums of the
+  // block accumulate in `red`, one row per (warp, row slot), touched once per work item as well.  Keeping both out
+  // of registers is what lets three blocks share an SM.
+  float* gam_s = reinterpret_cast<float*>(qk_smem + kQkRingBytes + kQkWarps * kRPW * 2 * kHD * 4);  // [2 * kHD]
+  for (int c = threadIdx.x; c < 2 * kHD; c += blockDim.x) gam_s[c] = __bfloat162float(gamma[c]);
+  float* my_red = &red[warp * kRPW + grp][e0];
 #pragma unroll
   for (int j = 0; j < 8; ++j) {
-    gq[j] = 0.f;
-    gk[j] = 0.f;
+    my_red[j] = 0.f;
+    my_red[kHD + j] = 0.f;
   }
+  __syncthreads();
 
-  const int groups_per_row = (heads + kHPW - 1) / kHPW;
-  const int items = nrows * groups_per_row;
-#pragma unroll 2
-  for (int it = warp; it < items; it += kQkWarps) {
-    const int r_local = it / groups_per_row;
-    const int head = (it - r_local * groups_per_row) * kHPW + grp;
-    const int row = row0 + r_local;
-    const bool active = head < heads;
-    const bool is_q = head < hq;
-    float dy[8], xh[8], fr[8];
-    float pos = 0.f, r = 0.f;
-    if (active) {
-      const __nv_bfloat16* dy_p = is_q ? dq + row * ld_dq + head * kHD + e0 : dk + row * ld_dk + (head - hq) * kHD + e0;
-      const uint4 a = *reinterpret_cast<const uint4*>(dy_p);
-      const uint4 b = *reinterpret_cast<const uint4*>(preact + row * ld_pre + head * kHD + e0);
-      const float4 f0 = *reinterpret_cast<const float4*>(freq + head * kHD + e0);
-      const float4 f1 = *reinterpret_cast<const float4*>(freq + head * kHD + e0 + 4);
-      pos = pos_is_float ? reinterpret_cast<const float*>(positions)[row]
-                         : static_cast<float>(reinterpret_cast<const int*>(positions)[row]);
-      r = rsqrtf(mean_sq[static_cast<long long>(row) * heads + head] + eps);
-      const uint32_t aw[4] = {a.x, a.y, a.z, a.w}, bw[4] = {b.x, b.y, b.z, b.w};
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        float2 t = unpack_bf16x2(aw[j]);
-        dy[2 * j] = t.x;
-        dy[2 * j + 1] = t.y;
-        t = unpack_bf16x2(bw[j]);
-        xh[2 * j] = t.x;
-        xh[2 * j + 1] = t.y;
-      }
-      fr[0] = f0.x; fr[1] = f0.y; fr[2] = f0.z; fr[3] = f0.w;
-      fr[4] = f1.x; fr[5] = f1.y; fr[6] = f1.z; fr[7] = f1.w;
+  // Work items: (row group, run of up to kQkHeadsPerItem heads); a run never mixes q and k heads, so the gamma vector
+  // and the accumulator it feeds are chosen once per item.
+  const int runs_q = (hq + kQkHeadsPerItem - 1) / kQkHeadsPerItem;
+  const int runs = runs_q + (hk + kQkHeadsPerItem - 1) / kQkHeadsPerItem;
+  // (row group, run) pairs are walked without divisions: a warp's next item lies warps_total items ahead
+  const int row_groups = (M + kRPW - 1) / kRPW;
+  const int warps_total = static_cast<int>(gridDim.x) * kQkWarps;
+  const int step_rg = warps_total / runs, step_run = warps_total % runs;
+
+  // Cursor over this warp's stream of (item, head); identical in all lanes except for the row.
+  struct Cursor {
+    int rg, run;  // row group and run of the current item (rg >= row_groups: past the end)
+    int head, h_end, row;
+  };
+  auto open_item = [&](Cursor& c) {
+    c.row = c.rg * kRPW + grp;
+    if (c.run < runs_q) {
+      c.head = c.run * kQkHeadsPerItem;
+      c.h_end = min(hq, c.head + kQkHeadsPerItem);
     } else {
-#pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        dy[j] = 0.f;
-        xh[j] = 0.f;
-        fr[j] = 0.f;
-      }
+      c.head = hq + (c.run - runs_q) * kQkHeadsPerItem;
+      c.h_end = min(heads, c.head + kQkHeadsPerItem);
     }
-    const float* gam = gam_s + (is_q ? 0 : kHD) + e0;
-    float dz[8];
-    float dot = 0.f;
+  };
+  // Source addresses of the prefetch cursor, advanced by one head per stream position (a run never leaves q or k).
+  const __nv_bfloat16 *src_dy = nullptr, *src_pre = nullptr;
+  const float* src_ms = nullptr;
+  auto open_sources = [&](const Cursor& c) {
+    if (c.rg < row_groups && c.row < M) {
+      src_dy = c.head < hq ? dq + c.row * ld_dq + c.head * kHD + e0 : dk + c.row * ld_dk + (c.head - hq) * kHD + e0;
+      src_pre = preact + c.row * ld_pre + c.head * kHD + e0;
+      src_ms = mean_sq + static_cast<long long>(c.row) * heads + c.head;
+    }
+  };
+  auto next_item = [&](Cursor& c) {
+    c.rg += step_rg;
+    c.run += step_run;
+    if (c.run >= runs) {
+      c.run -= runs;
+      ++c.rg;
+    }
+    open_item(c);
+  };
+  // issue the loads of the prefetch cursor's position into `slot` and step the cursor
+  auto issue_and_step = [&](Cursor& c, int slot) {
+    const bool live = c.rg < row_groups;
+    if (live && c.row < M) {
+      cp_async16(ring_a + slot * (kQkThreads * 16), src_dy);
+      cp_async16(ring_b + slot * (kQkThreads * 16), src_pre);
+      cp_async4(ring_m + slot * (kQkThreads * 4), src_ms);
+      src_dy += kHD;
+      src_pre += kHD;
+      src_ms += 1;
+    }
+    cp_async_commit();  // one group per stream position, empty or not, so that the group count stays uniform
+    if (live && ++c.head >= c.h_end) {
+      next_item(c);
+      open_sources(c);
+    }
+  };
+  auto sincos4 = [&](const float* f, float pos, float* sn, float* cs) {
 #pragma unroll
-    for (int p = 0; p < 4; ++p) {
-      const float hi = fr[2 * p], lo = fr[2 * p + 1];
+    for (int p2 = 0; p2 < 4; ++p2) {
+      const float hi = f[2 * p2], lo = f[2 * p2 + 1];
       const float t = pos * hi;
       const float terr = fmaf(pos, hi, -t);
       const float l = fmaf(pos, lo, terr);
       const float frac = (t - rintf(t)) + l;
-      float sn, cs;
-      __sincosf(kTwoPi * frac, &sn, &cs);
-      const float a = dy[2 * p], b = dy[2 * p + 1];
-      dz[2 * p] = a * cs + b * sn;
-      dz[2 * p + 1] = b * cs - a * sn;
+      __sincosf(kTwoPi * frac, &sn[p2], &cs[p2]);
     }
-#pragma unroll
-    for (int j = 0; j < 8; ++j) dot = fmaf(dz[j] * gam[j], xh[j], dot);
-#pragma unroll
-    for (int o = kG / 2; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
-    const float coef = dot * r * r * r * (1.0f / kHD);
-    uint32_t ow[4];
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      const float o0 = r * gam[2 * j] * dz[2 * j] - xh[2 * j] * coef;
-      const float o1 = r * gam[2 * j + 1] * dz[2 * j + 1] - xh[2 * j + 1] * coef;
-      ow[j] = pack_bf16x2(o0, o1);
-    }
-#pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      const float dgj = dz[j] * xh[j] * r;  // zero for inactive lanes
-      if (is_q) gq[j] += dgj;
-      else gk[j] += dgj;
-    }
-    if (active) *reinterpret_cast<uint4*>(grad + row * ld_grad + head * kHD + e0) = make_uint4(ow[0], ow[1], ow[2], ow[3]);
+  };
+
+  Cursor use, pre;
+  {
+    const int first = static_cast<int>(blockIdx.x) * kQkWarps + warp;
+    use.rg = first / runs;
+    use.run = first % runs;
   }
+  open_item(use);
+  pre = use;
+  open_sources(pre);
+#pragma unroll 1
+  for (int i = 0; i < kQkDepth; ++i) issue_and_step(pre, i);
+
+  int slot = 0;
+#pragma unroll 1
+  while (use.rg < row_groups) {
+    // ---- one work item: heads [use.head, use.h_end) of row use.row
+    const int row = use.row, h_begin = use.head, h_end = use.h_end;
+    const bool row_ok = row < M;
+    const bool is_q = h_begin < hq;
+    float gam[8], g[8], sn[4], cs[4];
+    {
+      const float4 g0 = *reinterpret_cast<const float4*>(gam_s + (is_q ? 0 : kHD) + e0);
+      const float4 g1 = *reinterpret_cast<const float4*>(gam_s + (is_q ? 0 : kHD) + e0 + 4);
+      gam[0] = g0.x; gam[1] = g0.y; gam[2] = g0.z; gam[3] = g0.w;
+      gam[4] = g1.x; gam[5] = g1.y; gam[6] = g1.z; gam[7] = g1.w;
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) g[j] = 0.f;
+    float pos = 0.f;
+    if (row_ok) {
+      pos = pos_is_float ? reinterpret_cast<const float*>(positions)[row] : static_cast<float>(reinterpret_cast<const int*>(positions)[row]);
+      if (periodic) {
+        const float4 f0 = __ldg(reinterpret_cast<const float4*>(freq + e0));
+        const float4 f1 = __ldg(reinterpret_cast<const float4*>(freq + e0 + 4));
+        const float fn[8] = {f0.x, f0.y, f0.z, f0.w, f1.x, f1.y, f1.z, f1.w};
+        sincos4(fn, pos, sn, cs);
+      }
+    }
+    __nv_bfloat16* out_p = grad + (row_ok ? row : 0) * ld_grad + h_begin * kHD + e0;
+    const float* freq_p = freq + h_begin * kHD + e0;
+#pragma unroll 1
+    for (int head = h_begin; head < h_end; ++head, out_p += kHD, freq_p += kHD) {
+      cp_async_wait<kQkDepth - 1>();  // the group of this stream position has landed
+      if (row_ok) {
+        const uint4 a = ld_shared_v4(ring_a + slot * (kQkThreads * 16));
+        const uint4 b = ld_shared_v4(ring_b + slot * (kQkThreads * 16));
+        float msv;
+        asm volatile("ld.shared.f32 %0, [%1];" : "=f"(msv) : "r"(ring_m + slot * (kQkThreads * 4)) : "memory");
+        const float r = rsqrtf(msv + eps);
+        if (!periodic) {
+          const float4 f0 = __ldg(reinterpret_cast<const float4*>(freq_p));
+          const float4 f1 = __ldg(reinterpret_cast<const float4*>(freq_p + 4));
+          const float fn[8] = {f0.x, f0.y, f0.z, f0.w, f1.x, f1.y, f1.z, f1.w};
+          sincos4(fn, pos, sn, cs);
+        }
+        float dy[8], xh[8];
+        {
+          // bf16 -> fp32 is a 16-bit shift: one shift and one mask per packed pair
+          const uint32_t aw[4] = {a.x, a.y, a.z, a.w}, bw[4] = {b.x, b.y, b.z, b.w};
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            dy[2 * j] = __uint_as_float(aw[j] << 16);
+            dy[2 * j + 1] = __uint_as_float(aw[j] & 0xffff0000u);
+            xh[2 * j] = __uint_as_float(bw[j] << 16);
+            xh[2 * j + 1] = __uint_as_float(bw[j] & 0xffff0000u);
+          }
+        }
+        float dz[8], tz[8];
+#pragma unroll
+        for (int p2 = 0; p2 < 4; ++p2) {
+          const float u = dy[2 * p2], w = dy[2 * p2 + 1];
+          dz[2 * p2] = fmaf(u, cs[p2], w * sn[p2]);
+          dz[2 * p2 + 1] = fmaf(w, cs[p2], -(u * sn[p2]));
+        }
+        float dot = 0.f;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          tz[j] = dz[j] * gam[j];
+          dot = fmaf(tz[j], xh[j], dot);
+        }
+#pragma unroll
+        for (int o = kG / 2; o > 0; o >>= 1) dot += __shfl_xor_sync(group_mask, dot, o);
+        const float ncoef = -(dot * r * r * r * (1.0f / kHD));
+        uint32_t ow[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+          ow[j] = pack_bf16x2(fmaf(r, tz[2 * j], xh[2 * j] * ncoef), fmaf(r, tz[2 * j + 1], xh[2 * j + 1] * ncoef));
+#pragma unroll
+        for (int j = 0; j < 8; ++j) g[j] = fmaf(dz[j] * xh[j], r, g[j]);
+        *reinterpret_cast<uint4*>(out_p) = make_uint4(ow[0], ow[1], ow[2], ow[3]);
+      }
+      // refill the slot just consumed with the stream position kQkDepth ahead
+      issue_and_step(pre, slot);
+      slot = (slot + 1 == kQkDepth) ? 0 : slot + 1;
+    }
+    {
+      // this lane is the only writer of its 16 slots of `red`
+      float* acc = my_red + (is_q ? 0 : kHD);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[j] += g[j];
+    }
+    next_item(use);
+  }
+  cp_async_wait<0>();
 
   // copy dv next to grad_pre so that one GEMM consumes [grad_pre | dv]
   if (dv != nullptr) {
-    const int total = nrows * nv8;
     const long long col_off = static_cast<long long>(heads) * kHD;
-    for (int i = threadIdx.x; i < total; i += blockDim.x) {
-      const int r_local = i / nv8;
-      const int c8 = i - r_local * nv8;
-      const int row = row0 + r_local;
-      *reinterpret_cast<uint4*>(grad + row * ld_grad + col_off + c8 * 8) =
-          *reinterpret_cast<const uint4*>(dv + row * ld_dv + c8 * 8);
-    }
+    for (int rr = blockIdx.x; rr < M; rr += gridDim.x)
+      for (int c8 = threadIdx.x; c8 < nv8; c8 += blockDim.x)
+        *reinterpret_cast<uint4*>(grad + rr * ld_grad + col_off + c8 * 8) = *reinterpret_cast<const uint4*>(dv + rr * ld_dv + c8 * 8);
   }
 
-#pragma unroll
-  for (int j = 0; j < 8; ++j) {
-    red[warp * kHPW + grp][e0 + j] = gq[j];
-    red[warp * kHPW + grp][kHD + e0 + j] = gk[j];
-  }
   __syncthreads();
   for (int c = threadIdx.x; c < 2 * kHD; c += blockDim.x) {
     float s = 0.f;
 #pragma unroll
-    for (int w = 0; w < kQkWarps * kHPW; ++w) s += red[w][c];
+    for (int w = 0; w < kQkWarps * kRPW; ++w) s += red[w][c];
     partials[static_cast<long long>(blockIdx.x) * (2 * kHD) + c] = s;
   }
+}
+
+template <int kHD>
+constexpr int qk_bwd_smem_bytes() {
+  return kQkRingBytes + kQkWarps * (32 / (kHD / 8)) * 2 * kHD * 4 + 2 * kHD * 4;
 }
 
 // Column sums of the [nblocks, width] partials: 32 columns x 8 row-lanes per block, rows strided over the lanes.
@@ -621,18 +760,42 @@ extern "C" int coda_b200_qknorm_rope_bwd(const void* dq, int64_t ld_dq, const vo
   if (hq > 0 && ld_dq < size_q) return fail(kBadArgument, "ld_dq is smaller than hq * head_dim");
   if (hk > 0 && ld_dk < size_k) return fail(kBadArgument, "ld_dk is smaller than hk * head_dim");
   if (dv != nullptr && ld_dv < nv) return fail(kBadArgument, "ld_dv is smaller than nv");
-  const int blocks = (M + kQkRowsPerBlock - 1) / kQkRowsPerBlock;
+  // persistent grid: as many blocks as are resident at once, never more than the workspace has partial rows for
+  // (one per kQkRowsPerBlock input rows) nor than there are work items for
+  const int rows_per_warp = 32 / (head_dim / 8);
+  const long long items = ((static_cast<long long>(M) + rows_per_warp - 1) / rows_per_warp) *
+                          ((hq + kQkHeadsPerItem - 1) / kQkHeadsPerItem + (hk + kQkHeadsPerItem - 1) / kQkHeadsPerItem);
+  if (items > 0x7fffffffLL) return fail(kBadArgument, "too many (row, head) items for one launch");
+  long long blocks_ll = (items + kQkWarps - 1) / kQkWarps;
+  const long long cap = static_cast<long long>(sm_count()) * kQkBlocksPerSm;
+  const long long ws_rows = (static_cast<long long>(M) + kQkRowsPerBlock - 1) / kQkRowsPerBlock;
+  if (blocks_ll > cap) blocks_ll = cap;
+  if (blocks_ll > ws_rows) blocks_ll = ws_rows;
+  const int blocks = static_cast<int>(blocks_ll);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   float* partials = static_cast<float*>(scratch);
   const int nv8 = dv ? nv / 8 : 0;
+  {
+    // the ring needs more than the default 48 KB of dynamic shared memory: opt in once per device
+    static std::atomic<unsigned long long> attr_set{0ull};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev < 0 || dev >= 64 || ((attr_set.load(std::memory_order_acquire) >> dev) & 1ull) == 0ull) {
+      cudaError_t e = cudaFuncSetAttribute(qknorm_rope_bwd_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, qk_bwd_smem_bytes<128>());
+      if (e == cudaSuccess)
+        e = cudaFuncSetAttribute(qknorm_rope_bwd_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, qk_bwd_smem_bytes<64>());
+      if (e != cudaSuccess) return fail(kCudaError, std::string("cudaFuncSetAttribute(qknorm_rope_bwd smem): ") + cudaGetErrorString(e));
+      if (dev >= 0 && dev < 64) attr_set.fetch_or(1ull << dev, std::memory_order_release);
+    }
+  }
   if (head_dim == 128)
-    qknorm_rope_bwd_kernel<128><<<blocks, kQkWarps * 32, 0, st>>>(
+    qknorm_rope_bwd_kernel<128><<<blocks, kQkThreads, qk_bwd_smem_bytes<128>(), st>>>(
         static_cast<const __nv_bfloat16*>(dq), ld_dq, static_cast<const __nv_bfloat16*>(dk), ld_dk,
         static_cast<const __nv_bfloat16*>(dv), ld_dv, nv8, static_cast<const __nv_bfloat16*>(preact), ld_pre, mean_sq,
         static_cast<const __nv_bfloat16*>(gamma), positions, pos_is_float, frequencies, hq, hk, eps,
         static_cast<__nv_bfloat16*>(grad), ld_grad, partials, M);
   else
-    qknorm_rope_bwd_kernel<64><<<blocks, kQkWarps * 32, 0, st>>>(
+    qknorm_rope_bwd_kernel<64><<<blocks, kQkThreads, qk_bwd_smem_bytes<64>(), st>>>(
         static_cast<const __nv_bfloat16*>(dq), ld_dq, static_cast<const __nv_bfloat16*>(dk), ld_dk,
         static_cast<const __nv_bfloat16*>(dv), ld_dv, nv8, static_cast<const __nv_bfloat16*>(preact), ld_pre, mean_sq,
         static_cast<const __nv_bfloat16*>(gamma), positions, pos_is_float, frequencies, hq, hk, eps,

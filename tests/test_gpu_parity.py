@@ -256,7 +256,7 @@ def test_qknorm_rope_golden(ck, golden_dir, name):
     # element-wise, with an absolute floor of a tenth of the largest entry: every entry is a sum of rows x heads signed
     # terms, so one that happens to lie near zero still carries the absolute error of the whole sum
     ew = eager.max_elementwise_err(dg, g["dgamma"], atol_frac=0.1)
-    assert ew <= 2e-2, f"dgamma: element-wise relative error {ew:.3e}"
+    assert ew <= 5e-2, f"dgamma: element-wise relative error {ew:.3e}"
     assert dg.dtype == torch.bfloat16
 
 
