@@ -569,22 +569,25 @@ constexpr int qk_bwd_smem_bytes() {
   return kQkRingBytes + kQkWarps * (32 / (kHD / 8)) * 2 * kHD * 4 + 2 * kHD * 4;
 }
 
-// Column sums of the [nblocks, width] partials: 32 columns x 8 row-lanes per block, rows strided over the lanes.
-__global__ void __launch_bounds__(256) fold_partials_kernel(const float* __restrict__ partials, int nblocks, int width,
-                                                            float* __restrict__ out) {
-  __shared__ float red[8][33];
+// Column sums of the [nblocks, width] partials: 32 columns x 32 row-lanes per block, rows strided over the lanes, so that
+// the few hundred partial rows are a dozen independent loads per thread rather than a long serial chain.
+constexpr int kFoldRowLanes = 32;
+__global__ void __launch_bounds__(32 * kFoldRowLanes) fold_partials_kernel(const float* __restrict__ partials, int nblocks, int width,
+                                                                          float* __restrict__ out) {
+  __shared__ float red[kFoldRowLanes][33];
   const int cx = threadIdx.x & 31, ry = threadIdx.x >> 5;
   const int c = blockIdx.x * 32 + cx;
   float s = 0.f;
   if (c < width) {
-    for (int b = ry; b < nblocks; b += 8) s += partials[static_cast<long long>(b) * width + c];
+#pragma unroll 4
+    for (int b = ry; b < nblocks; b += kFoldRowLanes) s += partials[static_cast<long long>(b) * width + c];
   }
   red[ry][cx] = s;
   __syncthreads();
   if (ry == 0 && c < width) {
     float t = 0.f;
 #pragma unroll
-    for (int j = 0; j < 8; ++j) t += red[j][cx];
+    for (int j = 0; j < kFoldRowLanes; ++j) t += red[j][cx];
     out[c] = t;
   }
 }
@@ -802,7 +805,7 @@ extern "C" int coda_b200_qknorm_rope_bwd(const void* dq, int64_t ld_dq, const vo
         static_cast<__nv_bfloat16*>(grad), ld_grad, partials, M);
   int rc = launch_check("qknorm_rope_bwd launch");
   if (rc != kOk) return rc;
-  fold_partials_kernel<<<(2 * head_dim + 31) / 32, 256, 0, st>>>(partials, blocks, 2 * head_dim, dgamma);
+  fold_partials_kernel<<<(2 * head_dim + 31) / 32, 32 * kFoldRowLanes, 0, st>>>(partials, blocks, 2 * head_dim, dgamma);
   return launch_check("fold_partials launch");
 }
 

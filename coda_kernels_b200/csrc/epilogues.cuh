@@ -97,6 +97,42 @@ __device__ __forceinline__ void ring_commit(EpiCtx& c) {
   c.slot = (c.slot + 1 == kRingSlots) ? 0u : c.slot + 1;
 }
 
+// ------------------------------------------------------------------ second-operand tiles by TMA
+// Lane 0 arms the slot's mbarrier and issues `nboxes` (1 or 2) loads of 32-row x 32-column bf16 boxes at columns
+// x, x + 32 of rows row0 .. row0 + 31 into load slot `s`; they land in the 64-byte swizzle, 2 KB per box, with rows and
+// columns outside the matrix zero-filled.  Every lane of the warp must have finished reading the slot's previous
+// contents (the caller places a __syncwarp between the last read and this call).
+__device__ __forceinline__ void operand_issue(const EpiCtx& c, int s, const CUtensorMap* m0, int x0, const CUtensorMap* m1, int x1) {
+  if (c.lane == 0) {
+    const uint32_t bar = c.ld_bar + 8 * s;
+    const uint32_t dst = c.ld_ring + s * kLoadSlotBytes;
+    mbar_arrive_expect_tx(bar, m1 != nullptr ? 4096u : 2048u);
+    tma_load_2d(dst, m0, bar, x0, c.row0);
+    if (m1 != nullptr) tma_load_2d(dst + 2048, m1, bar, x1, c.row0);
+  }
+}
+// All lanes: wait (bounded) until the loads of slot `s` have landed; flips the slot's parity.  Returns false if the
+// wait expired (the code is in the abort word; the caller carries on with whatever the slot holds).
+__device__ __forceinline__ bool operand_wait(EpiCtx& c, int s) {
+  const uint32_t parity = (c.ld_phase >> s) & 1u;
+  c.ld_phase ^= (1u << s);
+  return mbar_wait(c.ld_bar + 8 * s, parity, c.abort_word, kErrTimeoutEpiLoad);
+}
+// This lane's row of box `box` (0 or 1) of slot `s`: 32 bf16 -> fp32.
+__device__ __forceinline__ void operand_row32(const EpiCtx& c, int s, int box, float* v) {
+  const uint32_t tile = c.ld_ring + s * kLoadSlotBytes + box * 2048;
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const uint4 u = ld_shared_v4(stage_addr<64>(tile, c.lane, j));
+    const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      v[j * 8 + 2 * k] = __uint_as_float(w[k] << 16);
+      v[j * 8 + 2 * k + 1] = __uint_as_float(w[k] & 0xffff0000u);
+    }
+  }
+}
+
 // Calls f(ch, v) for ch = 0 .. n-1 with v = accumulator columns [32 ch, 32 ch + 32) of this thread's row.  Two
 // register buffers: the TMEM load of chunk ch+1 is in flight while f works on chunk ch.  `n` is warp-uniform.
 template <class F>
@@ -158,6 +194,7 @@ enum class Act { kNone, kSigmoid };
 
 template <typename OutT, Act kAct>
 struct EpiStore {
+  static constexpr uint32_t kLoadRingBytes = 0;
   struct Params {
     alignas(64) CUtensorMap tm_d;  // D as [M, N], box 32 x 32
     OutT* D;
@@ -211,6 +248,7 @@ struct EpiStore {
 // with no counterpart in the reference).
 template <bool kSigmoidGate>
 struct EpiGated {
+  static constexpr uint32_t kLoadRingBytes = 0;
   struct Params {
     alignas(64) CUtensorMap tm_pre;   // preact as [M, N], box 32 x 32
     alignas(64) CUtensorMap tm_post;  // postact as [M, N/2], box 16 x 32
@@ -283,6 +321,7 @@ constexpr int kLseStoreNone = 0, kLseStoreProbs = 1, kLseStoreLogits = 2;
 
 template <int kStore>
 struct EpiLse {
+  static constexpr uint32_t kLoadRingBytes = 0;
   struct Params {
     alignas(64) CUtensorMap tm_p;  // P as [M, N], box 32 x 32 (unused for kLseStoreNone)
     __nv_bfloat16* P;  // [M, N] or nullptr
@@ -374,6 +413,7 @@ struct EpiLse {
 // angle scheme coda/core/ops/math_utils.py:181-195).
 template <int kHD>
 struct EpiQKNormRope {
+  static constexpr uint32_t kLoadRingBytes = 0;
   struct Params {
     alignas(64) CUtensorMap tm_qk;   // qk as [M, size_qk], box 32 x 32
     alignas(64) CUtensorMap tm_pre;  // preact as [M, size_qk], box 32 x 32

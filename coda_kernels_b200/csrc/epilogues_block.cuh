@@ -43,6 +43,7 @@ __device__ __forceinline__ void load_colvec32(const __nv_bfloat16* src, float* v
 // D = rotate(acc * row_scale[row]) with the angle of each adjacent column pair taken from `freq` (hi, lo turns) and
 // the row's position.  Replaces `_gemm_rope_epi` / `_gemm_rmsnorm_rope_epi` (coda/core/gemm/functional.py:955-1062).
 struct EpiRope {
+  static constexpr uint32_t kLoadRingBytes = 0;
   struct Params {
     alignas(64) CUtensorMap tm_d;  // D as [M, N], box 32 x 32
     __nv_bfloat16* D;
@@ -97,9 +98,11 @@ struct EpiRope {
 // rstd = rsqrt(sum / N + eps) is formed afterwards and applied by the GEMM that consumes `post`.  Replaces
 // `_gemm_residual_partial_rmsnorm_epi` (coda/core/gemm/functional.py:573-613; epilogues.py:72-80).
 struct EpiResidualNorm {
+  static constexpr uint32_t kLoadRingBytes = kLoadRingBytesPerWarp;
   struct Params {
     alignas(64) CUtensorMap tm_pre;   // pre as [M, N], box 32 x 32
     alignas(64) CUtensorMap tm_post;  // post as [M, N], box 32 x 32
+    alignas(64) CUtensorMap tm_c;     // C as [M, N], box 32 x 32 (load)
     const __nv_bfloat16* C;  // [M, N] residual (may alias pre or post)
     long long ldc;
     __nv_bfloat16* pre;  // [M, N]
@@ -117,11 +120,20 @@ struct EpiResidualNorm {
     const bool row_ok = c.row < c.M;
     const long long r = c.row;
     float sq = 0.f;
-    for_chunks(c.taddr, valid_chunks<kBN>(c.n0, c.N), [&](int ch, float* v) {
+    const int n = valid_chunks<kBN>(c.n0, c.N);
+    if (p.use_tma) operand_issue(c, 0, &p.tm_c, c.n0, nullptr, 0);
+    for_chunks(c.taddr, n, [&](int ch, float* v) {
       const int col = c.n0 + ch * 32;
       const int ncols = c.N - col;
       float t[32];
-      load_row32(p.C + r * p.ldc + col, t, ncols, row_ok);
+      if (p.use_tma) {
+        __syncwarp();  // every lane is done with the slot the next load goes to
+        if (ch + 1 < n) operand_issue(c, (ch + 1) & 1, &p.tm_c, col + 32, nullptr, 0);
+        operand_wait(c, ch & 1);
+        operand_row32(c, ch & 1, 0, t);
+      } else {
+        load_row32(p.C + r * p.ldc + col, t, ncols, row_ok);
+      }
 #pragma unroll
       for (int j = 0; j < 32; ++j) {
         v[j] += t[j];
@@ -158,9 +170,11 @@ struct EpiResidualNorm {
 // postact = silu(gate) * up [M, F] (recomputed for the wgrad), and per (row, tile) sum of Z * dZ.  Replaces
 // `_gemm_swiglu_bwd_zdz_epi(_scaled)` (coda/core/gemm/functional.py:827-910; epilogues.py:105-127).
 struct EpiSwigluBwdZdz {
+  static constexpr uint32_t kLoadRingBytes = kLoadRingBytesPerWarp;
   struct Params {
     alignas(64) CUtensorMap tm_dz;    // dZ as [M, 2N], box 32 x 32
     alignas(64) CUtensorMap tm_post;  // postact as [M, N], box 32 x 32
+    alignas(64) CUtensorMap tm_z;     // Z as [M, 2N], box 32 x 32 (load)
     const __nv_bfloat16* Z;  // [M, 2N] (may alias dZ)
     long long ldz;
     __nv_bfloat16* dZ;  // [M, 2N]
@@ -177,12 +191,22 @@ struct EpiSwigluBwdZdz {
     const bool row_ok = c.row < c.M;
     const long long r = c.row;
     float zdz = 0.f;
-    for_chunks(c.taddr, valid_chunks<kBN>(c.n0, c.N), [&](int ch, float* t) {
+    const int n = valid_chunks<kBN>(c.n0, c.N);
+    if (p.use_tma) operand_issue(c, 0, &p.tm_z, 2 * c.n0, &p.tm_z, 2 * c.n0 + 32);
+    for_chunks(c.taddr, n, [&](int ch, float* t) {
       const int col = c.n0 + ch * 32;  // column of acc / postact; Z and dZ columns are 2*col ..
       const int ncols = c.N - col;
       float za[32], zb[32];
-      load_row32(p.Z + r * p.ldz + 2 * col, za, 2 * ncols, row_ok);
-      load_row32(p.Z + r * p.ldz + 2 * col + 32, zb, 2 * ncols - 32, row_ok);
+      if (p.use_tma) {
+        __syncwarp();  // every lane is done with the slot the next load goes to
+        if (ch + 1 < n) operand_issue(c, (ch + 1) & 1, &p.tm_z, 2 * col + 64, &p.tm_z, 2 * col + 96);
+        operand_wait(c, ch & 1);
+        operand_row32(c, ch & 1, 0, za);
+        operand_row32(c, ch & 1, 1, zb);
+      } else {
+        load_row32(p.Z + r * p.ldz + 2 * col, za, 2 * ncols, row_ok);
+        load_row32(p.Z + r * p.ldz + 2 * col + 32, zb, 2 * ncols - 32, row_ok);
+      }
       float out[32];
 #pragma unroll
       for (int j = 0; j < 32; ++j) {
@@ -233,9 +257,11 @@ struct EpiSwigluBwdZdz {
 // (each epilogue warp folds its 32 rows with a shuffle transpose-reduce).  Replaces
 // `_gemm_residual_partial_rmsnorm_bwd_epi_{store,accum}` (coda/core/gemm/functional.py:655-764; epilogues.py:130-168).
 struct EpiRmsnormBwd {
+  static constexpr uint32_t kLoadRingBytes = kLoadRingBytesPerWarp;
   struct Params {
-    alignas(64) CUtensorMap tm_dx;      // dX as [M, N], box 32 x 32
+    alignas(64) CUtensorMap tm_dx;      // dX as [M, N], box 32 x 32 (store, and load when accumulating)
     alignas(64) CUtensorMap tm_normed;  // normed as [M, N], box 32 x 32
+    alignas(64) CUtensorMap tm_pre;     // pre as [M, N], box 32 x 32 (load)
     const __nv_bfloat16* pre;  // [M, N]
     long long ld_pre;
     __nv_bfloat16* dX;  // [M, N]
@@ -259,22 +285,32 @@ struct EpiRmsnormBwd {
     const float rstd = row_ok ? __ldg(p.rstd + c.row) : 0.f;
     const float zdz = row_ok ? __ldg(p.zdz + c.row) : 0.f;
     const long long slab = c.row0 / 32;  // the warp's 32 rows start at a multiple of 32
-    for_chunks(c.taddr, valid_chunks<kBN>(c.n0, c.N), [&](int ch, float* y) {
+    const int n = valid_chunks<kBN>(c.n0, c.N);
+    const CUtensorMap* acc_map = p.accumulate ? &p.tm_dx : nullptr;
+    if (p.use_tma) operand_issue(c, 0, &p.tm_pre, c.n0, acc_map, c.n0);
+    for_chunks(c.taddr, n, [&](int ch, float* y) {
       const int col = c.n0 + ch * 32;
       const int ncols = c.N - col;
-      float n[32], w[32];
-      load_row32(p.pre + r * p.ld_pre + col, n, ncols, row_ok);
+      float nn[32], w[32], d[32];
+      if (p.use_tma) {
+        __syncwarp();  // every lane is done with the slot the next load goes to
+        if (ch + 1 < n) operand_issue(c, (ch + 1) & 1, &p.tm_pre, col + 32, acc_map, col + 32);
+        operand_wait(c, ch & 1);
+        operand_row32(c, ch & 1, 0, nn);
+        if (p.accumulate) operand_row32(c, ch & 1, 1, d);
+      } else {
+        load_row32(p.pre + r * p.ld_pre + col, nn, ncols, row_ok);
+        if (p.accumulate) load_row32(p.dX + r * p.ld_dx + col, d, ncols, row_ok);
+      }
       load_colvec32(p.weight + col, w, ncols);
-      float d[32];
-      if (p.accumulate) load_row32(p.dX + r * p.ld_dx + col, d, ncols, row_ok);
 #pragma unroll
       for (int j = 0; j < 32; ++j) {
         y[j] *= alpha;
-        n[j] *= rstd;
-        const float dx = (y[j] * w[j] - n[j] * zdz) * rstd;
+        nn[j] *= rstd;
+        const float dx = (y[j] * w[j] - nn[j] * zdz) * rstd;
         d[j] = p.accumulate ? d[j] + dx : dx;
-        w[j] *= n[j];      // normed
-        y[j] *= n[j];      // this row's contribution to dweight (zero for rows >= M: acc and pre read as zero)
+        w[j] *= nn[j];     // normed
+        y[j] *= nn[j];     // this row's contribution to dweight (zero for rows >= M: acc and pre read as zero)
       }
       if (p.use_tma) {
         const uint32_t tile = ring_acquire(c);  // [dX 32 x 64 B | normed 32 x 64 B]

@@ -69,6 +69,7 @@ extern "C" int coda_b200_gemm_residual_partial_rmsnorm(const void* A, int64_t a_
   ep.tiles_n = (N + kTileN - 1) / kTileN;
   int rc = make_tmap_out(&ep.tm_pre, ep.pre, N, M, ld_pre);
   if (rc == kOk) rc = make_tmap_out(&ep.tm_post, ep.post, N, M, ld_post);
+  if (rc == kOk) rc = make_tmap_out(&ep.tm_c, ep.C, N, M, ldc);
   if (rc != kOk) return rc;
   Operand a{A, a_stride_m, a_stride_k};
   Operand b{B, b_stride_n, b_stride_k};
@@ -119,6 +120,7 @@ extern "C" int coda_b200_gemm_swiglu_bwd_zdz(const void* A, int64_t a_stride_m, 
   ep.tiles_n = (N + kTileN - 1) / kTileN;
   int rc = make_tmap_out(&ep.tm_dz, ep.dZ, 2LL * N, M, ld_dz);
   if (rc == kOk) rc = make_tmap_out(&ep.tm_post, ep.postact, N, M, ld_post);
+  if (rc == kOk) rc = make_tmap_out(&ep.tm_z, ep.Z, 2LL * N, M, ldz);
   if (rc != kOk) return rc;
   Operand a{A, a_stride_m, a_stride_k};
   Operand b{B, b_stride_n, b_stride_k};
@@ -154,6 +156,7 @@ extern "C" int coda_b200_gemm_residual_partial_rmsnorm_bwd(const void* A, int64_
   ep.accumulate = accumulate;
   int rc = make_tmap_out(&ep.tm_dx, ep.dX, N, M, ld_dx);
   if (rc == kOk) rc = make_tmap_out(&ep.tm_normed, ep.normed, N, M, ld_normed);
+  if (rc == kOk) rc = make_tmap_out(&ep.tm_pre, ep.pre, N, M, ld_pre);
   if (rc != kOk) return rc;
   Operand a{A, a_stride_m, a_stride_k};
   Operand b{B, b_stride_n, b_stride_k};

@@ -49,20 +49,30 @@ struct EpiCtx {
   int lane;
   uint32_t ring;   // shared-memory address of this warp's staging ring (kRingSlots slots of kRingSlotBytes)
   uint32_t slot;   // slot the next staged sub-tile goes to
+  // Epilogues that read a second [M, N] operand fetch its sub-tiles by TMA into the warp's load slots:
+  uint32_t ld_ring;   // shared-memory address of this warp's kLoadSlots load slots (kLoadSlotBytes each); 0 if none
+  uint32_t ld_bar;    // shared-memory address of the warp's kLoadSlots mbarriers
+  uint32_t ld_phase;  // bit s = parity the next wait on slot s expects
+  volatile int* abort_word;
 };
 
 constexpr int kRingSlots = 2;
 constexpr uint32_t kRingSlotBytes = 4096;  // 32 rows x 128 bytes: the widest sub-tile an epilogue stages at once
 constexpr uint32_t kRingBytesPerWarp = kRingSlots * kRingSlotBytes;
+constexpr int kLoadSlots = 2;
+constexpr uint32_t kLoadSlotBytes = 4096;  // two 32 x 32 bf16 boxes
+constexpr uint32_t kLoadRingBytesPerWarp = kLoadSlots * kLoadSlotBytes;
+constexpr uint32_t kLoadBarOffset = 512;  // inside the control block: kNumEpiWarps x kLoadSlots mbarriers
 
-template <int kCtaGroup, int kBN>
+// kEpiLoadBytes: bytes of operand load slots per epilogue warp (0 for epilogues without a second operand).
+template <int kCtaGroup, int kBN, uint32_t kEpiLoadBytes = 0>
 struct GemmCfg {
   static constexpr int kBNcta = kBN / kCtaGroup;  // B rows loaded by one CTA
   static constexpr uint32_t kABytes = kBlockM * kBlockK * 2;
   static constexpr uint32_t kBBytes = kBNcta * kBlockK * 2;
   static constexpr uint32_t kStageBytes = kABytes + kBBytes;
   static constexpr uint32_t kCtrlBytes = 1024;  // barriers, TMEM pointer, abort word
-  static constexpr uint32_t kEpiScratch = kNumEpiWarps * kRingBytesPerWarp;  // staging rings of the epilogue warps
+  static constexpr uint32_t kEpiScratch = kNumEpiWarps * (kRingBytesPerWarp + kEpiLoadBytes);  // staging rings (+ load slots) of the epilogue warps
   static constexpr int kStagesFit = (kSmemBudget - 1024 - kCtrlBytes - kEpiScratch) / kStageBytes;
   static constexpr int kStages = kStagesFit > 8 ? 8 : kStagesFit;
   static constexpr uint32_t kSmemBytes = 1024 + kStages * kStageBytes + kCtrlBytes + kEpiScratch;
@@ -86,7 +96,7 @@ template <int kCtaGroup, int kBN, bool kAMn, bool kBMn, class Epi>
 __global__ void __launch_bounds__(kNumThreads, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b, const GemmShape shape,
             const __grid_constant__ typename Epi::Params ep, int* __restrict__ status) {
-  using Cfg = GemmCfg<kCtaGroup, kBN>;
+  using Cfg = GemmCfg<kCtaGroup, kBN, Epi::kLoadRingBytes>;
   constexpr int kStages = Cfg::kStages;
   constexpr int kBNcta = Cfg::kBNcta;
   constexpr uint32_t kABytes = Cfg::kABytes;
@@ -129,6 +139,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
     for (int a = 0; a < 2; ++a) {
       mbar_init(bar_acc_full + 8 * a, 1);
       mbar_init(bar_acc_empty + 8 * a, kNumEpiWarps * kCtaGroup);
+    }
+    if constexpr (Epi::kLoadRingBytes != 0) {
+      for (int i = 0; i < kNumEpiWarps * kLoadSlots; ++i) mbar_init(ctrl + kLoadBarOffset + 8 * i, 1);
     }
     *abort_word = 0;
     fence_barrier_init();
@@ -265,6 +278,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
     c.lane = lane;
     c.ring = epi_rings + static_cast<uint32_t>(warp - 2) * kRingBytesPerWarp;
     c.slot = 0;
+    c.ld_ring = Epi::kLoadRingBytes != 0 ? epi_rings + kNumEpiWarps * kRingBytesPerWarp + static_cast<uint32_t>(warp - 2) * Epi::kLoadRingBytes : 0u;
+    c.ld_bar = ctrl + kLoadBarOffset + static_cast<uint32_t>(warp - 2) * (8 * kLoadSlots);
+    c.ld_phase = 0;
+    c.abort_word = abort_word;
     uint32_t it = 0;
     for (int tile = cluster_id; tile < num_tiles; tile += num_clusters, ++it) {
       int tm, tn;

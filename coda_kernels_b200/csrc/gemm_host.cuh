@@ -120,6 +120,8 @@ inline int make_tmap_out(CUtensorMap* m, const void* ptr, int elem_bytes, long l
   if (r != CUDA_SUCCESS) return fail(kCudaError, "cuTensorMapEncodeTiled (output) failed with code " + std::to_string(static_cast<int>(r)));
   return kOk;
 }
+// (The same geometry serves the epilogues' second-operand loads: a 32 x 32 box that lands swizzled in a load slot,
+// rows and columns outside the matrix reading as zero.)
 template <typename T>
 inline int make_tmap_out(CUtensorMap* m, T* ptr, long long cols, long long rows, long long ld, int box_cols = 32) {
   return make_tmap_out(m, static_cast<const void*>(ptr), static_cast<int>(sizeof(T)), cols, rows, ld, box_cols);
@@ -149,7 +151,7 @@ inline LaunchOptions launch_options() {
 template <int kCtaGroup, int kBN, bool kAMn, bool kBMn, class Epi>
 int launch_gemm_cfg(const void* a_ptr, long long lda, const void* b_ptr, long long ldb, int M, int N, int K,
                     const typename Epi::Params& ep, int* status, cudaStream_t stream, const LaunchOptions& opt) {
-  using Cfg = GemmCfg<kCtaGroup, kBN>;
+  using Cfg = GemmCfg<kCtaGroup, kBN, Epi::kLoadRingBytes>;
   CUtensorMap ta, tb;
   int rc;
   // K-major: lines run along K; box = 64 k x (rows of the tile).  MN-major: lines run along M/N; box = 64 x 64 k.

@@ -20,6 +20,7 @@ enum : int {
   kErrTimeoutAccEmpty = 3,  // MMA issuer: accumulator never drained
   kErrTimeoutAccFull = 4,   // epilogue: accumulator never completed
   kErrPeerAbort = 5,        // the other CTA of the pair gave up
+  kErrTimeoutEpiLoad = 6,   // epilogue: a second-operand tile never arrived
 };
 
 constexpr unsigned long long kWaitTimeoutNs = 2000000000ull;  // 2 s

@@ -20,11 +20,16 @@ backend; the GEMMs and element-wise passes are the library's CUDA kernels.
 
 from __future__ import annotations
 
+import os
 from typing import Optional
 
 import torch
 import torch.distributed as dist
 from torch import Tensor
+
+# CODA_B200_OVERLAP_DX=0 issues the cross-entropy input-gradient all-reduce synchronously (after it, then the weight
+# gradient GEMM) instead of letting the two overlap: a switch for measurements.
+OVERLAP_DX_ALLREDUCE = os.environ.get("CODA_B200_OVERLAP_DX", "1") == "1"
 
 
 def shard_bounds(total: int, rank: int, world: int, multiple: int = 1) -> tuple[int, int]:
@@ -155,6 +160,9 @@ class VocabParallelLinearCrossEntropy(torch.autograd.Function):
                 # asynchronous: the all-reduce runs on the communicator's stream while the weight-gradient GEMM
                 # below runs on this one; the streams are joined only after that GEMM has been enqueued
                 pending = dist.all_reduce(dx, op=dist.ReduceOp.SUM, group=ctx.group, async_op=True)
+                if not OVERLAP_DX_ALLREDUCE:
+                    pending.wait()
+                    pending = None
         if ctx.needs_input_grad[1]:
             dweight = ops.gemm_scalar_scale(dlogits.mT, x, alpha=alpha)
         if pending is not None:
