@@ -34,6 +34,12 @@ struct GemmShape {
   int tiles_m;  // number of (kBlockM * kCtaGroup)-row tiles
   int tiles_n;  // number of kBN-column tiles
   int group_m;  // raster: tiles of `group_m` consecutive row-tiles share their column sweep (L2 reuse)
+  // Measurement aid (0 = off): while the mainloop of a tile runs, each epilogue warp issues this many bytes of
+  // coalesced global loads from [probe_src, probe_src + probe_span) and of shared-memory stores per k-block, i.e. the
+  // load/store-unit traffic an operand-transforming prologue would add, without changing any result.
+  int probe_ld_bytes, probe_st_bytes;
+  const void* probe_src;
+  long long probe_span;
 };
 
 // Per-thread view of one accumulator tile handed to an epilogue.  `ring` and `slot` describe the warp's private
@@ -90,6 +96,33 @@ __device__ __forceinline__ void tile_coords(const GemmShape& s, int tile, int& t
   const int r = tile - g * per_group;
   tm = first_m + r % gsz;
   tn = r / gsz;
+}
+
+// What-if traffic for the prologue-fusion study (see GemmShape): runs in an epilogue warp while it would otherwise
+// spin on the accumulator barrier, stops as soon as the accumulator is complete.
+__device__ __forceinline__ void probe_lsu_traffic(const GemmShape& shape, const EpiCtx& c, uint32_t bar, uint32_t parity, int num_kb,
+                                                  int warp_slot) {
+  if (c.lane == 0) tma_store_wait_read<0>();  // the staging ring doubles as the store target
+  __syncwarp();
+  const uint4* src = static_cast<const uint4*>(shape.probe_src);
+  const long long n16 = shape.probe_span / 16;
+  const int ld_iters = shape.probe_ld_bytes / 512, st_iters = shape.probe_st_bytes / 512;
+  long long pos = (static_cast<long long>(blockIdx.x) * kNumEpiWarps + warp_slot) * 65536 % (n16 > 64 ? n16 - 64 : 1);
+  uint4 acc = make_uint4(0u, 0u, 0u, 0u);
+#pragma unroll 1
+  for (int kb = 0; kb < num_kb; ++kb) {
+    if (mbar_try_wait(bar, parity)) break;
+#pragma unroll 4
+    for (int i = 0; i < ld_iters; ++i) {
+      const uint4 v = __ldcg(src + pos + c.lane);
+      acc.x ^= v.x; acc.y ^= v.y; acc.z ^= v.z; acc.w ^= v.w;
+      pos += 32;
+      if (pos + 32 >= n16) pos = 0;
+    }
+#pragma unroll 4
+    for (int i = 0; i < st_iters; ++i) st_shared_v4(c.ring + ((i * 512 + c.lane * 16) & (kRingBytesPerWarp - 1)), acc.x, acc.y, acc.z, acc.w);
+  }
+  __syncwarp();
 }
 
 template <int kCtaGroup, int kBN, bool kAMn, bool kBMn, class Epi>
@@ -287,6 +320,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
       int tm, tn;
       tile_coords(shape, tile, tm, tn);
       const uint32_t acc = it & 1u, aph = (it >> 1) & 1u;
+      if (shape.probe_ld_bytes + shape.probe_st_bytes != 0) probe_lsu_traffic(shape, c, bar_acc_full + 8 * acc, aph, num_kb, warp - 2);
       bool ok = mbar_wait(bar_acc_full + 8 * acc, aph, abort_word, kErrTimeoutAccFull);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) {

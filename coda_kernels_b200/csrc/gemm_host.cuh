@@ -36,6 +36,10 @@ struct Options {
   std::atomic<int> max_ctas{0};   // cap on the persistent grid; 0 = all SMs
   std::atomic<int> tile_n{0};     // 0 = choose per problem; 64, 128 or 256 forces the column-tile width where it is built
   std::atomic<int> epi_tma{1};    // 1 = epilogues stage their output in shared memory and store it with TMA; 0 = per-thread stores
+  // Measurement aid: KB of extra global loads / shared stores per k-block and CTA issued by the epilogue warps while the
+  // mainloop runs (the traffic an operand-transforming prologue would add); results are unaffected.  0 = off.
+  std::atomic<int> probe_ld_kb{0};
+  std::atomic<int> probe_st_kb{0};
 };
 inline Options& options() {
   static Options o;
@@ -141,11 +145,12 @@ inline int sm_count() {
 
 // The options one launch works with, read once.
 struct LaunchOptions {
-  int cta_group, group_m, max_ctas, tile_n, epi_tma;
+  int cta_group, group_m, max_ctas, tile_n, epi_tma, probe_ld_kb, probe_st_kb;
 };
 inline LaunchOptions launch_options() {
   const Options& o = options();
-  return LaunchOptions{o.cta_group.load(), o.group_m.load(), o.max_ctas.load(), o.tile_n.load(), o.epi_tma.load()};
+  return LaunchOptions{o.cta_group.load(), o.group_m.load(), o.max_ctas.load(), o.tile_n.load(),
+                       o.epi_tma.load(),   o.probe_ld_kb.load(), o.probe_st_kb.load()};
 }
 
 template <int kCtaGroup, int kBN, bool kAMn, bool kBMn, class Epi>
@@ -170,6 +175,12 @@ int launch_gemm_cfg(const void* a_ptr, long long lda, const void* b_ptr, long lo
   shape.tiles_m = (M + tile_m - 1) / tile_m;
   shape.tiles_n = (N + kBN - 1) / kBN;
   shape.group_m = opt.group_m > 0 ? opt.group_m : (kCtaGroup == 2 ? 8 : 16);
+  // per epilogue warp (four per CTA) and k-block, in bytes, rounded down to whole 512-byte warp accesses
+  shape.probe_ld_bytes = opt.probe_ld_kb * 1024 / kNumEpiWarps / 512 * 512;
+  shape.probe_st_bytes = opt.probe_st_kb * 1024 / kNumEpiWarps / 512 * 512;
+  shape.probe_src = a_ptr;
+  shape.probe_span = static_cast<long long>(M) * K * 2;  // the A operand's own bytes (valid for either major when densely packed)
+  if ((kAMn ? lda != M : lda != K)) shape.probe_ld_bytes = 0;  // strided operand: no dense span to read from
   const long long num_tiles = static_cast<long long>(shape.tiles_m) * shape.tiles_n;
   if (num_tiles <= 0 || num_tiles > 0x7fffffffLL) return fail(kBadArgument, "tile count out of range");
 

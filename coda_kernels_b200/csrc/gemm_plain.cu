@@ -27,6 +27,9 @@ extern "C" int coda_b200_set_option(const char* name, int value) {
   } else if (!strcmp(name, "epi_tma")) {
     if (value != 0 && value != 1) return fail(kBadArgument, "epi_tma must be 0 or 1");
     o.epi_tma = value;
+  } else if (!strcmp(name, "probe_ld_kb") || !strcmp(name, "probe_st_kb")) {
+    if (value < 0 || value > 256) return fail(kBadArgument, "probe traffic must be between 0 and 256 KB per k-block");
+    (name[6] == 'l' ? o.probe_ld_kb : o.probe_st_kb) = value;
   } else {
     return fail(kBadArgument, std::string("unknown option: ") + name);
   }

@@ -47,6 +47,10 @@ const char* coda_b200_last_error(void);
  * stores, the default; 0 = per-thread 16-byte stores).  Options are
  * process-wide atomics: a launch reads them once at its start, so changing one
  * from another host thread is safe and affects later launches only.
+ * "probe_ld_kb" / "probe_st_kb" (0 = off) are a measurement aid: KB of extra
+ * global loads / shared-memory stores per k-block and CTA that the epilogue
+ * warps issue while a GEMM's mainloop runs, to measure what the load/store
+ * traffic of an operand-transforming prologue would cost; results are unchanged.
  * Returns 0, or CODA_B200_EARG for an unknown name or value. */
 int coda_b200_set_option(const char* name, int value);
 

@@ -95,3 +95,29 @@ def test_vocab_parallel_lse_exchange_two_ranks(tmp_path):
     mp.spawn(_lse_worker, args=(2, _free_port(), str(out)), nprocs=2, join=True)
     ok, loss, ref = out.read_text().split()
     assert ok == "1", f"sharded loss {loss} vs oracle {ref}"
+
+
+def test_block_wrappers_flatten_and_restore_batched_activations():
+    """The layer blocks take ``[batch, length, dim]`` activations as the reference does and hand the kernels 2-D views."""
+    from coda_kernels_b200.blocks import llama3
+
+    x = torch.zeros(2, 3, 8, dtype=torch.bfloat16)
+    flat = llama3._tokens(x)
+    assert flat.shape == (6, 8) and flat.data_ptr() == x.data_ptr()
+    assert llama3._like(torch.zeros(6, 5), x).shape == (2, 3, 5)
+    assert llama3._like(torch.zeros(6, 5), flat).shape == (6, 5)
+    with pytest.raises(AssertionError):  # LM-head targets must be int32, as in the reference
+        w = torch.zeros(8, 8, dtype=torch.bfloat16)
+        llama3.block_post(x, x, w, torch.zeros(16, 8, dtype=torch.bfloat16), w, w, torch.zeros(8, dtype=torch.bfloat16),
+                          torch.zeros(8, dtype=torch.bfloat16), torch.zeros(6, dtype=torch.int64), 1e-5)
+
+
+def test_runtime_reads_model_args_like_the_reference():
+    import types
+
+    from coda.runtime import CodaRuntime
+
+    rt = CodaRuntime(types.SimpleNamespace(n_heads=32, n_kv_heads=None, dim=4096, norm_eps=1e-5, n_layers=4))
+    assert (rt.num_heads, rt.num_kv_heads, rt.head_dim, rt.num_layers) == (32, 32, 128, 4)
+    rt = CodaRuntime(types.SimpleNamespace(n_heads=32, n_kv_heads=8, dim=4096, norm_eps=1e-5, n_layers=4))
+    assert rt.num_kv_heads == 8 and abs(rt.attention_scale - 128 ** -0.5) < 1e-12
