@@ -697,6 +697,12 @@ def measure_op(b: Bench, op: str, headline: bool) -> tuple[dict, dict]:
     return res, extra
 
 
+def _native_dispatch() -> bool:
+    from coda_kernels_b200 import ops
+
+    return ops._native is not None
+
+
 def main() -> None:
     _claim_stdout()
     ap = argparse.ArgumentParser()
@@ -762,6 +768,7 @@ def main() -> None:
             "data": "synthetic",
             "config": {"workload": head["workload"], **s, "global_batch_tokens": s["M"], "parallelism": head["parallelism"],
                        "dx_reduction": head["dx_reduction"], "cuda_graph": head["cuda_graph"], "l2": head["l2"],
+                       "dispatch": "TORCH_LIBRARY shim (libcoda_b200_torch.so)" if _native_dispatch() else "ctypes custom ops",
                        "timing": f"median of {head['windows']} windows of {args.steps} steps, max over ranks per window"},
             "tokens_per_s": head["tokens_per_s"], "frac_of_peak": head["frac_of_peak"],
             "frac_of_sustained_peak": head["frac_of_sustained_peak"],

@@ -14,6 +14,7 @@ from pathlib import Path
 
 _PKG_DIR = Path(__file__).resolve().parent
 LIB_PATH = _PKG_DIR / "libcoda_b200.so"
+NATIVE_LIB_PATH = _PKG_DIR / "libcoda_b200_torch.so"  # TORCH_LIBRARY dispatch shim over the same C ABI (see ops.py)
 
 _P = c_void_p
 _I = c_int

@@ -1,9 +1,12 @@
-"""Builds ``libcoda_b200.so`` in-tree with nvcc for sm_100a.
+"""Builds ``libcoda_b200.so`` in-tree with nvcc for sm_100a, and the PyTorch dispatch shim next to it.
 
 Run as ``python -m coda_kernels_b200.build``; ``build_library()`` is also what
 ``__graft_entry__.build()`` calls.  Each ``csrc/*.cu`` is compiled to an object
 file (in parallel) and the objects are linked into one shared library that sits
 next to this file, so that the binary travels with the source tree.
+``csrc_torch/torch_binding.cpp`` (TORCH_LIBRARY registrations that call the C
+ABI) is compiled with g++ against the installed torch into
+``libcoda_b200_torch.so``, which links ``libcoda_b200.so`` by ``$ORIGIN``.
 """
 
 from __future__ import annotations
@@ -20,6 +23,8 @@ from pathlib import Path
 PKG_DIR = Path(__file__).resolve().parent
 CSRC = PKG_DIR / "csrc"
 LIB_PATH = PKG_DIR / "libcoda_b200.so"
+TORCH_SRC = PKG_DIR / "csrc_torch" / "torch_binding.cpp"
+TORCH_LIB_PATH = PKG_DIR / "libcoda_b200_torch.so"
 HASH_PATH = PKG_DIR / "libcoda_b200.srchash"
 OBJ_DIR = PKG_DIR / "build"
 
@@ -53,7 +58,7 @@ def _sources() -> list[Path]:
 def source_hash() -> str:
     """Digest of every file the library is built from (content, not mtime: copies of the tree keep it)."""
     h = hashlib.sha256()
-    files = sorted(CSRC.glob("*.cu")) + sorted(CSRC.glob("*.cuh")) + [PKG_DIR.parent / "include" / "coda_b200.h"]
+    files = sorted(CSRC.glob("*.cu")) + sorted(CSRC.glob("*.cuh")) + [PKG_DIR.parent / "include" / "coda_b200.h", TORCH_SRC]
     for f in files:
         h.update(f.name.encode())
         h.update(f.read_bytes())
@@ -62,7 +67,7 @@ def source_hash() -> str:
 
 
 def is_stale() -> bool:
-    if not LIB_PATH.exists() or not HASH_PATH.exists():
+    if not LIB_PATH.exists() or not TORCH_LIB_PATH.exists() or not HASH_PATH.exists():
         return True
     return HASH_PATH.read_text().strip() != source_hash()
 
@@ -108,8 +113,26 @@ def _build_locked(nvcc: str, force: bool, verbose: bool) -> Path:
     res = subprocess.run(link, capture_output=True, text=True)
     if res.returncode != 0:
         raise RuntimeError(f"link failed:\n{res.stdout}\n{res.stderr}")
+    _build_torch_shim()
     HASH_PATH.write_text(source_hash() + "\n")
     return LIB_PATH
+
+
+def _build_torch_shim() -> None:
+    """g++ only: the shim holds no device code.  It is linked against the torch of this interpreter."""
+    import torch
+    from torch.utils import cpp_extension
+
+    cxx = shutil.which("g++") or "g++"
+    cuda_home = os.environ.get("CUDA_HOME", "/usr/local/cuda")
+    cmd = [cxx, "-O2", "-std=c++17", "-fPIC", "-shared", f"-D_GLIBCXX_USE_CXX11_ABI={int(torch._C._GLIBCXX_USE_CXX11_ABI)}",
+           str(TORCH_SRC), "-o", str(TORCH_LIB_PATH)]
+    cmd += [f"-I{p}" for p in cpp_extension.include_paths()] + [f"-I{cuda_home}/include"]
+    cmd += [f"-L{p}" for p in cpp_extension.library_paths()] + ["-ltorch", "-ltorch_cpu", "-lc10", "-lc10_cuda", "-ltorch_cuda"]
+    cmd += [f"-L{PKG_DIR}", f"-l:{LIB_PATH.name}", "-Wl,-rpath,$ORIGIN"]
+    res = subprocess.run(cmd, capture_output=True, text=True)
+    if res.returncode != 0:
+        raise RuntimeError(f"building {TORCH_LIB_PATH.name} failed:\n{res.stdout}\n{res.stderr}")
 
 
 if __name__ == "__main__":

@@ -287,6 +287,95 @@ for _op in (
     _op.register_fake(_noop_fake)
 
 
+# ------------------------------------------------------------------------------------------------ compiled dispatch
+# The same ten device operators registered from C++ (csrc_torch/torch_binding.cpp, namespace ``coda_b200n``): a
+# TORCH_LIBRARY shim over the same C ABI that skips the per-launch Python work of the ctypes ops above.  Eager calls
+# go through it; while ``torch.compile`` traces, the Python custom ops above are used (opaque to the tracer, and
+# dispatch cost is irrelevant there).  ``CODA_B200_DISPATCH=ctypes`` keeps every call on the ctypes binding.
+_native = None
+if os.environ.get("CODA_B200_DISPATCH", "native") != "ctypes":
+    if not _lib_module.NATIVE_LIB_PATH.exists():
+        raise ImportError(
+            f"{_lib_module.NATIVE_LIB_PATH} is missing: build it with `python -m coda_kernels_b200.build` "
+            "(or set CODA_B200_DISPATCH=ctypes to use the ctypes binding of the same kernels)")
+    torch.ops.load_library(str(_lib_module.NATIVE_LIB_PATH))
+    _native = torch.ops.coda_b200n
+    for _name in ("gemm_out", "gemm_sigmoid_out", "gemm_swiglu_out", "gemm_lse_out", "lse_finalize_out", "ce_grad_fixup_",
+                  "gemm_qknorm_rope_out", "dswiglu_out", "dsigmoid_out", "qknorm_rope_bwd_out"):
+        torch.library.register_fake(f"coda_b200n::{_name}")(_noop_fake)
+
+    def _use_native() -> bool:
+        return not torch.compiler.is_compiling()
+
+    _ct_gemm_out, _ct_gemm_sigmoid_out, _ct_gemm_swiglu_out, _ct_gemm_lse_out = _gemm_out, _gemm_sigmoid_out, _gemm_swiglu_out, _gemm_lse_out
+    _ct_lse_finalize_out, _ct_ce_grad_fixup, _ct_gemm_qknorm_rope_out = _lse_finalize_out, _ce_grad_fixup, _gemm_qknorm_rope_out
+    _ct_dswiglu_out, _ct_dsigmoid_out, _ct_qknorm_rope_bwd_out = _dswiglu_out, _dsigmoid_out, _qknorm_rope_bwd_out
+
+    def _gemm_out(A, B, out, alpha, C=None):  # noqa: F811
+        if _use_native():
+            _native.gemm_out(A, B, out, alpha, C, status_word(A.device))
+        else:
+            _ct_gemm_out(A, B, out, alpha, C)
+
+    def _gemm_sigmoid_out(A, B, out):  # noqa: F811
+        if _use_native():
+            _native.gemm_sigmoid_out(A, B, out, status_word(A.device))
+        else:
+            _ct_gemm_sigmoid_out(A, B, out)
+
+    def _gemm_swiglu_out(A, B, preact, postact):  # noqa: F811
+        if _use_native():
+            _native.gemm_swiglu_out(A, B, preact, postact, status_word(A.device))
+        else:
+            _ct_gemm_swiglu_out(A, B, preact, postact)
+
+    def _gemm_lse_out(A, B, probs, part_max, part_sum, target, target_logit):  # noqa: F811
+        if _use_native():
+            _native.gemm_lse_out(A, B, probs, part_max, part_sum, target, target_logit, status_word(A.device))
+        else:
+            _ct_gemm_lse_out(A, B, probs, part_max, part_sum, target, target_logit)
+
+    def _lse_finalize_out(part_max, part_sum, target, target_logit, ignore_index, lse, losses):  # noqa: F811
+        if _use_native():
+            _native.lse_finalize_out(part_max, part_sum, target, target_logit, ignore_index, lse, losses)
+        else:
+            _ct_lse_finalize_out(part_max, part_sum, target, target_logit, ignore_index, lse, losses)
+
+    def _ce_grad_fixup(probs, part_max, lse, target, ignore_index):  # noqa: F811
+        if _use_native():
+            _native.ce_grad_fixup_(probs, part_max, lse, target, ignore_index)
+        else:
+            _ct_ce_grad_fixup(probs, part_max, lse, target, ignore_index)
+
+    def _gemm_qknorm_rope_out(A, B, qk, preact, v, mean_sq, gamma, positions, frequencies, head_dim, num_heads_q, num_heads_k, eps):  # noqa: F811
+        if _use_native():
+            _native.gemm_qknorm_rope_out(A, B, qk, preact, v, mean_sq, gamma, positions, frequencies, head_dim, num_heads_q,
+                                         num_heads_k, eps, status_word(A.device))
+        else:
+            _ct_gemm_qknorm_rope_out(A, B, qk, preact, v, mean_sq, gamma, positions, frequencies, head_dim, num_heads_q, num_heads_k, eps)
+
+    def _dswiglu_out(preact, dout, grad_pre):  # noqa: F811
+        if _use_native():
+            _native.dswiglu_out(preact, dout, grad_pre)
+        else:
+            _ct_dswiglu_out(preact, dout, grad_pre)
+
+    def _dsigmoid_out(out, dout, grad_pre):  # noqa: F811
+        if _use_native():
+            _native.dsigmoid_out(out, dout, grad_pre)
+        else:
+            _ct_dsigmoid_out(out, dout, grad_pre)
+
+    def _qknorm_rope_bwd_out(dq, dk, dv, preact, mean_sq, gamma, positions, frequencies, head_dim, num_heads_q, num_heads_k, eps,  # noqa: F811
+                             grad, dgamma, scratch):
+        if _use_native():
+            _native.qknorm_rope_bwd_out(dq, dk, dv, preact, mean_sq, gamma, positions, frequencies, head_dim, num_heads_q, num_heads_k,
+                                        eps, grad, dgamma, scratch)
+        else:
+            _ct_qknorm_rope_bwd_out(dq, dk, dv, preact, mean_sq, gamma, positions, frequencies, head_dim, num_heads_q, num_heads_k, eps,
+                                    grad, dgamma, scratch)
+
+
 # ------------------------------------------------------------------------------------------------ python wrappers
 
 

@@ -273,6 +273,9 @@ int64_t coda_b200_qknorm_rope_bwd_scratch_bytes(int M, int head_dim);
  * grad[:, :(hq+hk)*d] and, if dv != NULL, copies dv [M, nv] into
  * grad[:, (hq+hk)*d:], so that one GEMM over `grad` yields dx and one yields
  * dW.  dgamma fp32 [2*d].  `scratch` holds per-block partial sums of dgamma.
+ * Every leading dimension must cover its row (ld_dq >= hq*d, ld_dk >= hk*d,
+ * ld_dv >= nv, ld_pre >= (hq+hk)*d, ld_grad >= (hq+hk)*d + nv): rows are read
+ * and written with 16-byte accesses, a short stride returns CODA_B200_EARG.
  * Replaces `qknorm_rope_bwd` (coda/core/elementwise/functional.py:314-456;
  * kernel coda/core/elementwise/rope.py:19-253). */
 int coda_b200_qknorm_rope_bwd(const void* dq, int64_t ld_dq, const void* dk, int64_t ld_dk, const void* dv, int64_t ld_dv,
@@ -294,7 +297,9 @@ int coda_b200_qknorm_rope_bwd(const void* dq, int64_t ld_dq, const void* dk, int
  *     that device current); make that first call before any stream capture;
  *   - all calls share the array, which keeps the previous call's contents (each
  *     call overwrites every entry it later reads, so nothing needs clearing);
- *     two calls that overlap on the GPU (different streams) race on it. */
+ *     two calls that overlap on the GPU (different streams) race on it;
+ *   - the array used is the current device's: a call whose `grad` buffer lives
+ *     on another GPU returns CODA_B200_EARG instead of launching. */
 int coda_b200_qknorm_rope_bwd_noalloc(const void* dq, int64_t ld_dq, const void* dk, int64_t ld_dk, const void* dv,
                                       int64_t ld_dv, int nv, const void* preact, int64_t ld_pre, const float* mean_sq,
                                       const void* gamma, const void* positions, int pos_is_float, const float* frequencies,
