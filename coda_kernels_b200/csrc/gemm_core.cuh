@@ -111,7 +111,7 @@ __device__ __forceinline__ void probe_lsu_traffic(const GemmShape& shape, const 
   uint4 acc = make_uint4(0u, 0u, 0u, 0u);
 #pragma unroll 1
   for (int kb = 0; kb < num_kb; ++kb) {
-    if (mbar_try_wait(bar, parity)) break;
+    if (mbar_test_wait(bar, parity)) break;
 #pragma unroll 4
     for (int i = 0; i < ld_iters; ++i) {
       const uint4 v = __ldcg(src + pos + c.lane);

@@ -307,6 +307,24 @@ if os.environ.get("CODA_B200_DISPATCH", "native") != "ctypes":
     def _use_native() -> bool:
         return not torch.compiler.is_compiling()
 
+    class _Native:
+        """``torch.ops.coda_b200n`` with argument errors re-raised as the package's own exception type, so both bindings
+        report a rejected call the same way."""
+
+        def __getattr__(self, name):
+            op = getattr(torch.ops.coda_b200n, name)
+
+            def call(*args):
+                try:
+                    op(*args)
+                except RuntimeError as ex:
+                    raise _lib_module.CodaB200Error(str(ex).split("\n")[0]) from None
+
+            setattr(self, name, call)
+            return call
+
+    _native = _Native()
+
     _ct_gemm_out, _ct_gemm_sigmoid_out, _ct_gemm_swiglu_out, _ct_gemm_lse_out = _gemm_out, _gemm_sigmoid_out, _gemm_swiglu_out, _gemm_lse_out
     _ct_lse_finalize_out, _ct_ce_grad_fixup, _ct_gemm_qknorm_rope_out = _lse_finalize_out, _ce_grad_fixup, _gemm_qknorm_rope_out
     _ct_dswiglu_out, _ct_dsigmoid_out, _ct_qknorm_rope_bwd_out = _dswiglu_out, _dsigmoid_out, _qknorm_rope_bwd_out
@@ -461,11 +479,24 @@ def lse_finalize(part_max: Tensor, part_sum: Tensor, target: Tensor, target_logi
     return lse, losses
 
 
+_DEBUG_CHECKS = os.environ.get("CODA_B200_SYNC_STATUS", "0") == "1" or os.environ.get("CODA_B200_DEBUG", "0") == "1"
+
+
+def _debug_check_targets(target: Tensor, num_classes: int, ignore_index: int) -> None:
+    """Debug mode only (it synchronises): a label outside ``[0, num_classes)`` that is not ``ignore_index`` would pick no
+    logit and give a silently wrong loss (the reference does not check either)."""
+    if _DEBUG_CHECKS and not torch.compiler.is_compiling():
+        bad = (target != ignore_index) & ((target < 0) | (target >= num_classes))
+        if bool(bad.any()):
+            raise ValueError(f"target holds labels outside [0, {num_classes}) that are not ignore_index={ignore_index}")
+
+
 def gemm_lse_select_logits(A: Tensor, B: Tensor, target: Tensor, ignore_index: int) -> tuple[Tensor, Tensor, Tensor]:
     """Per-row ``(loss, lse, target_logit)`` without storing anything of size [M, N].
 
     Counterpart of ``gemm_lse_select_logits`` (coda/core/gemm/functional.py:496-527).
     """
+    _debug_check_targets(target, B.shape[1], ignore_index)
     _, part_max, part_sum, target_logit = gemm_lse_partials(A, B, target, store_probs=False)
     lse, losses = lse_finalize(part_max, part_sum, target, target_logit, ignore_index)
     return losses, lse, target_logit
@@ -479,6 +510,7 @@ def gemm_lse_dlogits(A: Tensor, B: Tensor, target: Tensor, ignore_index: int) ->
     unnormalised probabilities first and the gradient after the in-place pass,
     never the logits.
     """
+    _debug_check_targets(target, B.shape[1], ignore_index)
     probs, part_max, part_sum, target_logit = gemm_lse_partials(A, B, target, store_probs=True)
     lse, losses = lse_finalize(part_max, part_sum, target, target_logit, ignore_index)
     _ce_grad_fixup(probs, part_max, lse, target, int(ignore_index))
