@@ -491,21 +491,32 @@ struct EpiQKNormRope {
         } else if (row_ok) {
           store_row32(prow + ch * 32, v, 32);
         }
+        // gamma and the (hi, lo) frequency pairs of these 32 columns: the same addresses in every lane, 16 bytes per load
 #pragma unroll
-        for (int j = 0; j < 16; ++j) {
-          const int e = ch * 32 + 2 * j;  // element index inside the head
-          const float2 g = unpack_bf16x2(__ldg(reinterpret_cast<const unsigned int*>(gam + e)));
-          const float2 f = __ldg(reinterpret_cast<const float2*>(p.freq + col0 + e));
-          const float y0 = v[2 * j] * g.x * r;
-          const float y1 = v[2 * j + 1] * g.y * r;
-          const float t = pos * f.x;
-          const float terr = fmaf(pos, f.x, -t);
-          const float l = fmaf(pos, f.y, terr);
-          const float frac = (t - rintf(t)) + l;
-          float sn, cs;
-          __sincosf(kTwoPi * frac, &sn, &cs);
-          v[2 * j] = y0 * cs - y1 * sn;
-          v[2 * j + 1] = y0 * sn + y1 * cs;
+        for (int q4 = 0; q4 < 4; ++q4) {
+          const int e8 = ch * 32 + q4 * 8;  // element index inside the head
+          const uint4 g4 = __ldg(reinterpret_cast<const uint4*>(gam + e8));
+          const uint32_t gw[4] = {g4.x, g4.y, g4.z, g4.w};
+#pragma unroll
+          for (int h2 = 0; h2 < 2; ++h2) {
+            const float4 f4 = __ldg(reinterpret_cast<const float4*>(p.freq + col0 + e8 + 4 * h2));
+            const float fh[2] = {f4.x, f4.z}, fl[2] = {f4.y, f4.w};
+#pragma unroll
+            for (int k = 0; k < 2; ++k) {
+              const int j = q4 * 4 + h2 * 2 + k;
+              const float2 g = unpack_bf16x2(gw[h2 * 2 + k]);
+              const float y0 = v[2 * j] * g.x * r;
+              const float y1 = v[2 * j + 1] * g.y * r;
+              const float t = pos * fh[k];
+              const float terr = fmaf(pos, fh[k], -t);
+              const float l = fmaf(pos, fl[k], terr);
+              const float frac = (t - rintf(t)) + l;
+              float sn, cs;
+              __sincosf(kTwoPi * frac, &sn, &cs);
+              v[2 * j] = y0 * cs - y1 * sn;
+              v[2 * j + 1] = y0 * sn + y1 * cs;
+            }
+          }
         }
         if (p.use_tma) {
           stage_row_bf16<32>(tile + 2048, c.lane, v);

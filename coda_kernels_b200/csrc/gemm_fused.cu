@@ -186,8 +186,8 @@ extern "C" int coda_b200_gemm_rmsnorm_qknorm_rope(const void* A, int64_t a_strid
   if (ld_qk % 8 || ld_pre % 8 || ld_qk < size_qk || ld_pre < size_qk) return fail(kBadArgument, "bad qk / preact leading dimension");
   if (v != nullptr && (ld_v % 8 || ld_v < N - size_qk || !aligned16(v))) return fail(kBadArgument, "bad v leading dimension / alignment");
   if (!aligned16(qk) || !aligned16(preact)) return fail(kBadArgument, "outputs must be 16-byte aligned");
-  if ((reinterpret_cast<uintptr_t>(frequencies) & 7u) || (reinterpret_cast<uintptr_t>(gamma) & 3u))
-    return fail(kBadArgument, "frequencies must be 8-byte and gamma 4-byte aligned");
+  if ((reinterpret_cast<uintptr_t>(frequencies) & 15u) || (reinterpret_cast<uintptr_t>(gamma) & 15u))
+    return fail(kBadArgument, "frequencies and gamma must be 16-byte aligned");
   Operand a{A, a_stride_m, a_stride_k};
   Operand b{B, b_stride_n, b_stride_k};
   if (head_dim == 128)

@@ -517,6 +517,13 @@ def gemm_lse_dlogits(A: Tensor, B: Tensor, target: Tensor, ignore_index: int) ->
     return losses, probs
 
 
+def _aligned16(t: Tensor) -> Tensor:
+    """Contiguous and 16-byte aligned (the kernels read small vectors such as gamma and the frequencies 16 bytes at a
+    time): a view that starts at an odd offset is copied."""
+    t = t.contiguous()
+    return t if t.data_ptr() % 16 == 0 else t.clone()
+
+
 def gemm_qknorm_rope(
     A: Tensor, B: Tensor, weight: Tensor, positions: Tensor, frequencies: Tensor, head_dim: int, num_heads_q: int,
     num_heads_k: int, eps: float,
@@ -542,7 +549,7 @@ def gemm_qknorm_rope(
     mean_sq = torch.empty(M, heads, dtype=torch.float32, device=A.device)
     v = torch.empty(M, N - size_qk, dtype=A.dtype, device=A.device) if N > size_qk else None
     _gemm_qknorm_rope_out(
-        A, B, qk, preact, v, mean_sq, weight.contiguous(), positions.contiguous(), frequencies.contiguous(), head_dim,
+        A, B, qk, preact, v, mean_sq, _aligned16(weight), positions.contiguous(), _aligned16(frequencies), head_dim,
         num_heads_q, num_heads_k, float(eps),
     )
     return qk, preact, mean_sq, v
@@ -582,7 +589,7 @@ def qknorm_rope_bwd(
     blocks = (M + _QK_BWD_ROWS_PER_BLOCK - 1) // _QK_BWD_ROWS_PER_BLOCK  # = coda_b200_qknorm_rope_bwd_scratch_bytes / (8 * head_dim)
     scratch = torch.empty(blocks * 2 * head_dim, dtype=torch.float32, device=x.device)
     _qknorm_rope_bwd_out(
-        dq, dk, dv, x, head_mean_sq, gamma.contiguous(), pos.contiguous(), freq.contiguous(), head_dim, num_heads_q,
+        dq, dk, dv, x, head_mean_sq, _aligned16(gamma), pos.contiguous(), _aligned16(freq), head_dim, num_heads_q,
         num_heads_k, float(eps), grad, dgamma, scratch,
     )
     return grad, dgamma

@@ -14,7 +14,7 @@ import torch
 from torch import Tensor
 
 from ._lib import check, lib
-from .ops import _ce_grad_fixup, _noop_fake, _require, _require_cuda_bf16, _stream, lse_finalize, lse_tiles, status_word
+from .ops import _aligned16, _ce_grad_fixup, _noop_fake, _require, _require_cuda_bf16, _stream, lse_finalize, lse_tiles, status_word
 
 
 def _check_rstd(rstd: Tensor, M: int) -> None:
@@ -140,7 +140,7 @@ def gemm_rmsnorm_qknorm_rope(
     mean_sq = torch.empty(M, heads, dtype=torch.float32, device=A.device)
     v = torch.empty(M, N - size_qk, dtype=A.dtype, device=A.device) if N > size_qk else None
     _gemm_rmsnorm_qknorm_rope_out(
-        A, B, rstd, qk, preact, v, mean_sq, weight.contiguous(), positions.contiguous(), frequencies.contiguous(), head_dim,
+        A, B, rstd, qk, preact, v, mean_sq, _aligned16(weight), positions.contiguous(), _aligned16(frequencies), head_dim,
         num_heads_q, num_heads_k, float(eps),
     )
     return qk, preact, mean_sq, v
