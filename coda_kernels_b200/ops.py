@@ -521,6 +521,8 @@ def _aligned16(t: Tensor) -> Tensor:
     """Contiguous and 16-byte aligned (the kernels read small vectors such as gamma and the frequencies 16 bytes at a
     time): a view that starts at an odd offset is copied."""
     t = t.contiguous()
+    if torch.compiler.is_compiling():  # addresses are not visible to the tracer; traced callers pass whole tensors
+        return t
     return t if t.data_ptr() % 16 == 0 else t.clone()
 
 
