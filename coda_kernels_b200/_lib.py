@@ -29,6 +29,7 @@ SIGNATURES = {
     "coda_b200_selftest_wait_timeout": (_I, [_P, _L, _P, _P]),
     "coda_b200_gemm": (_I, [_P, _L, _L, _P, _L, _L, _P, _L, _I, _I, _I, _I, _P, _P, _P]),
     "coda_b200_gemm_add": (_I, [_P, _L, _L, _P, _L, _L, _P, _L, _I, _P, _L, _I, _I, _I, _I, _P, _P, _P]),
+    "coda_b200_gemm_dsigmoid_dgrad": (_I, [_P, _L, _P, _L, _P, _L, _P, _L, _P, _L, _I, _I, _I, _P, _P]),
     "coda_b200_gemm_sigmoid": (_I, [_P, _L, _L, _P, _L, _L, _P, _L, _I, _I, _I, _I, _P, _P]),
     "coda_b200_gemm_swiglu": (_I, [_P, _L, _L, _P, _L, _L, _P, _L, _P, _L, _I, _I, _I, _P, _P]),
     "coda_b200_gemm_sigmoid_glu": (_I, [_P, _L, _L, _P, _L, _L, _P, _L, _P, _L, _I, _I, _I, _P, _P]),

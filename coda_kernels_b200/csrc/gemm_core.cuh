@@ -69,14 +69,16 @@ constexpr int kLoadSlots = 2;
 constexpr uint32_t kLoadSlotBytes = 4096;  // two 32 x 32 bf16 boxes
 constexpr uint32_t kLoadRingBytesPerWarp = kLoadSlots * kLoadSlotBytes;
 constexpr uint32_t kLoadBarOffset = 512;  // inside the control block: kNumEpiWarps x kLoadSlots mbarriers
+constexpr uint32_t kRawBarOffset = 256;   // inside the control block: one mbarrier per stage for a prologue's raw tiles
 
 // kEpiLoadBytes: bytes of operand load slots per epilogue warp (0 for epilogues without a second operand).
-template <int kCtaGroup, int kBN, uint32_t kEpiLoadBytes = 0>
+// kStageExtraBytes: bytes a prologue policy adds to every pipeline stage (the raw tile it transforms with).
+template <int kCtaGroup, int kBN, uint32_t kEpiLoadBytes = 0, uint32_t kStageExtraBytes = 0>
 struct GemmCfg {
   static constexpr int kBNcta = kBN / kCtaGroup;  // B rows loaded by one CTA
   static constexpr uint32_t kABytes = kBlockM * kBlockK * 2;
   static constexpr uint32_t kBBytes = kBNcta * kBlockK * 2;
-  static constexpr uint32_t kStageBytes = kABytes + kBBytes;
+  static constexpr uint32_t kStageBytes = kABytes + kBBytes + kStageExtraBytes;
   static constexpr uint32_t kCtrlBytes = 1024;  // barriers, TMEM pointer, abort word
   static constexpr uint32_t kEpiScratch = kNumEpiWarps * (kRingBytesPerWarp + kEpiLoadBytes);  // staging rings (+ load slots) of the epilogue warps
   static constexpr int kStagesFit = (kSmemBudget - 1024 - kCtrlBytes - kEpiScratch) / kStageBytes;
@@ -125,11 +127,53 @@ __device__ __forceinline__ void probe_lsu_traffic(const GemmShape& shape, const 
   __syncwarp();
 }
 
-template <int kCtaGroup, int kBN, bool kAMn, bool kBMn, class Epi>
-__global__ void __launch_bounds__(kNumThreads, 1)
+// ------------------------------------------------------------------ A-operand prologues
+// A prologue policy replaces the TMA load of the A operand by "transform warps" (warps 6..9) that build each 128 x 64
+// K-major A tile themselves and write it into the pipeline stage in the swizzle the MMA expects.
+struct ProNone {
+  static constexpr int kWarps = 0;
+  static constexpr uint32_t kStageExtraBytes = 0;
+  struct Params {};
+};
+
+// G = dout * out * (1 - out), the gradient of a sigmoid through its stored output, formed on the fly as the A operand
+// of the input-gradient GEMM dx = G @ W (coda/kernels/functional/sigmoid.py:33-38 does this as a separate aten pass).
+// TMA loads the `out` tile straight into the stage's A slot (it has the operand's layout already) and the `dout`
+// tile into an extra slot of the stage; the transform warps multiply in place.  Math in packed bf16 (three roundings
+// instead of one) to stay within the issue budget of four warps per k-block.  The CTAs of column tile 0 also store
+// G, for the weight-gradient GEMM that follows.
+struct ProDSigmoid {
+  static constexpr int kWarps = 4;
+  static constexpr uint32_t kStageExtraBytes = kBlockM * kBlockK * 2;  // the dout tile
+  struct Params {
+    alignas(64) CUtensorMap tm_dout;  // dout as [M, Kc], box 64 x 128, 128-byte swizzle (the A operand's geometry)
+    __nv_bfloat16* G;                 // [M, Kc] written once
+    long long ld_g;
+  };
+  // 8 consecutive elements (16 bytes) of out and dout -> 8 elements of G
+  __device__ static uint4 transform(const uint4& o, const uint4& d) {
+    const __nv_bfloat162 one = __float2bfloat162_rn(1.0f);
+    const uint32_t ow[4] = {o.x, o.y, o.z, o.w}, dw[4] = {d.x, d.y, d.z, d.w};
+    uint32_t r[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const __nv_bfloat162 ov = *reinterpret_cast<const __nv_bfloat162*>(&ow[j]);
+      const __nv_bfloat162 dv = *reinterpret_cast<const __nv_bfloat162*>(&dw[j]);
+      const __nv_bfloat162 g = __hmul2(__hmul2(dv, ov), __hsub2(one, ov));
+      r[j] = *reinterpret_cast<const uint32_t*>(&g);
+    }
+    return make_uint4(r[0], r[1], r[2], r[3]);
+  }
+};
+
+template <int kCtaGroup, int kBN, bool kAMn, bool kBMn, class Epi, class Pro = ProNone>
+__global__ void __launch_bounds__(kNumThreads + Pro::kWarps * 32, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b, const GemmShape shape,
-            const __grid_constant__ typename Epi::Params ep, int* __restrict__ status) {
-  using Cfg = GemmCfg<kCtaGroup, kBN, Epi::kLoadRingBytes>;
+            const __grid_constant__ typename Epi::Params ep, int* __restrict__ status,
+            const __grid_constant__ typename Pro::Params pp) {
+  using Cfg = GemmCfg<kCtaGroup, kBN, Epi::kLoadRingBytes, Pro::kStageExtraBytes>;
+  constexpr bool kProlog = Pro::kWarps > 0;
+  static_assert(!kProlog || !kAMn, "transform warps build a K-major A tile");
   constexpr int kStages = Cfg::kStages;
   constexpr int kBNcta = Cfg::kBNcta;
   constexpr uint32_t kABytes = Cfg::kABytes;
@@ -166,7 +210,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
     prefetch_tmap(&tmap_a);
     prefetch_tmap(&tmap_b);
     for (int s = 0; s < kStages; ++s) {
-      mbar_init(bar_full + 8 * s, 1);
+      mbar_init(bar_full + 8 * s, 1 + Pro::kWarps * kCtaGroup);  // the producer's expect_tx arrive + one per transform warp of the pair
       mbar_init(bar_empty + 8 * s, 1);
     }
     for (int a = 0; a < 2; ++a) {
@@ -175,6 +219,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
     }
     if constexpr (Epi::kLoadRingBytes != 0) {
       for (int i = 0; i < kNumEpiWarps * kLoadSlots; ++i) mbar_init(ctrl + kLoadBarOffset + 8 * i, 1);
+    }
+    if constexpr (kProlog) {
+      for (int i = 0; i < kStages; ++i) mbar_init(ctrl + kRawBarOffset + 8 * i, 1);  // this CTA's raw tiles have landed
     }
     *abort_word = 0;
     fence_barrier_init();
@@ -208,12 +255,19 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
             ok = false;
             break;
           }
-          if (leader) mbar_arrive_expect_tx(bar_full + 8 * s, kStageBytes * kCtaGroup);
+          if (leader) mbar_arrive_expect_tx(bar_full + 8 * s, (kProlog ? Cfg::kBBytes : kStageBytes) * kCtaGroup);
           const uint32_t a_dst = smem_base + s * kStageBytes;
           const uint32_t b_dst = a_dst + kABytes;
           const uint32_t sig = full_sig + 8 * s;
           const int k0 = kb * kBlockK;
-          if constexpr (!kAMn) {
+          if constexpr (kProlog) {
+            // raw tiles for the transform warps: `out` into the A slot, `dout` into the stage's extra slot, both of this
+            // CTA's own rows, signalled on this CTA's own barrier (plain loads, not the pair form)
+            const uint32_t raw_bar = ctrl + kRawBarOffset + 8 * s;
+            mbar_arrive_expect_tx(raw_bar, 2 * kABytes);
+            tma_load_2d(a_dst, &tmap_a, raw_bar, k0, a_row0);
+            tma_load_2d(a_dst + kABytes + Cfg::kBBytes, &pp.tm_dout, raw_bar, k0, a_row0);
+          } else if constexpr (!kAMn) {
             if constexpr (kCtaGroup == 2) tma_load_2d_pair(a_dst, &tmap_a, sig, k0, a_row0);
             else tma_load_2d(a_dst, &tmap_a, sig, k0, a_row0);
           } else {
@@ -301,6 +355,52 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
       if (!ok) abort_notify_and_drain(peer_abort, *abort_word);
     }
     __syncwarp();
+  } else if (kProlog && warp >= 2 + kNumEpiWarps) {
+    // ============================================================ transform warps (A-operand prologue)
+    if constexpr (kProlog) {
+      const int t = warp - (2 + kNumEpiWarps);  // rows 32 t .. 32 t + 31 of the CTA's A tile
+      const int piece = lane & 7;               // 16-byte piece = 8 contraction columns
+      const int rsub = lane >> 3;               // 4 rows per access
+      const uint32_t full_sig = (kCtaGroup == 2) ? mapa(bar_full, 0) : bar_full;  // the leader's barriers
+      const int Kc = shape.K;
+      uint32_t s = 0, ph = 0;
+      bool ok = true;
+      for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters) {
+        int tm, tn;
+        tile_coords(shape, tile, tm, tn);
+        const int a_row0 = tm * (kBlockM * kCtaGroup) + static_cast<int>(rank) * kBlockM;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(ctrl + kRawBarOffset + 8 * s, ph, abort_word, kErrTimeoutFull)) {
+            ok = false;
+            break;
+          }
+          const uint32_t a_dst = smem_base + s * kStageBytes;
+          const uint32_t x_dst = a_dst + kABytes + Cfg::kBBytes;
+          const int k0 = kb * kBlockK;
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const int r_in = 32 * t + 4 * i + rsub;
+            const uint32_t off = r_in * 128 + ((piece ^ (r_in & 7)) << 4);  // the operand's 128-byte swizzle
+            const uint4 g = Pro::transform(ld_shared_v4(a_dst + off), ld_shared_v4(x_dst + off));
+            st_shared_v4(a_dst + off, g.x, g.y, g.z, g.w);  // in place: the A slot now holds G
+            const int row = a_row0 + r_in, col = k0 + piece * 8;
+            if (tn == 0 && row < shape.M && col < Kc) *reinterpret_cast<uint4*>(pp.G + static_cast<long long>(row) * pp.ld_g + col) = g;
+          }
+          fence_proxy_async_smem();  // the tensor core reads the tile through the async proxy
+          __syncwarp();
+          if (lane == 0) {
+            if constexpr (kCtaGroup == 2) mbar_arrive_cluster(full_sig + 8 * s);
+            else mbar_arrive(bar_full + 8 * s);
+          }
+          if (++s == kStages) {
+            s = 0;
+            ph ^= 1u;
+          }
+        }
+      }
+      if (!ok && lane == 0) abort_notify_and_drain(peer_abort, *abort_word);
+      __syncwarp();
+    }
   } else {
     // ============================================================ epilogue
     const int q = warp & 3;  // TMEM lane quadrant this warp may read

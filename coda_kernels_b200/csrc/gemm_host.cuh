@@ -153,18 +153,21 @@ inline LaunchOptions launch_options() {
                        o.epi_tma.load(),   o.probe_ld_kb.load(), o.probe_st_kb.load()};
 }
 
-template <int kCtaGroup, int kBN, bool kAMn, bool kBMn, class Epi>
+// With a prologue policy (`Pro`, see gemm_core.cuh) `a_ptr` is the raw matrix that TMA loads into the A slot and the
+// transform warps rewrite in place; `pp` carries what else they need.
+template <int kCtaGroup, int kBN, bool kAMn, bool kBMn, class Epi, class Pro = ProNone>
 int launch_gemm_cfg(const void* a_ptr, long long lda, const void* b_ptr, long long ldb, int M, int N, int K,
-                    const typename Epi::Params& ep, int* status, cudaStream_t stream, const LaunchOptions& opt) {
-  using Cfg = GemmCfg<kCtaGroup, kBN, Epi::kLoadRingBytes>;
+                    const typename Epi::Params& ep, int* status, cudaStream_t stream, const LaunchOptions& opt,
+                    const typename Pro::Params& pp = {}) {
+  using Cfg = GemmCfg<kCtaGroup, kBN, Epi::kLoadRingBytes, Pro::kStageExtraBytes>;
   CUtensorMap ta, tb;
   int rc;
   // K-major: lines run along K; box = 64 k x (rows of the tile).  MN-major: lines run along M/N; box = 64 x 64 k.
-  if (!kAMn) rc = make_tmap_bf16(&ta, a_ptr, K, M, lda, kBlockM);
-  else rc = make_tmap_bf16(&ta, a_ptr, M, K, lda, kBlockK);
-  if (rc != kOk) return rc;
   if (!kBMn) rc = make_tmap_bf16(&tb, b_ptr, K, N, ldb, Cfg::kBNcta);
   else rc = make_tmap_bf16(&tb, b_ptr, N, K, ldb, kBlockK);
+  if (rc != kOk) return rc;
+  if (!kAMn) rc = make_tmap_bf16(&ta, a_ptr, K, M, lda, kBlockM);
+  else rc = make_tmap_bf16(&ta, a_ptr, M, K, lda, kBlockK);
   if (rc != kOk) return rc;
 
   GemmShape shape;
@@ -184,7 +187,7 @@ int launch_gemm_cfg(const void* a_ptr, long long lda, const void* b_ptr, long lo
   const long long num_tiles = static_cast<long long>(shape.tiles_m) * shape.tiles_n;
   if (num_tiles <= 0 || num_tiles > 0x7fffffffLL) return fail(kBadArgument, "tile count out of range");
 
-  auto kern = gemm_kernel<kCtaGroup, kBN, kAMn, kBMn, Epi>;
+  auto kern = gemm_kernel<kCtaGroup, kBN, kAMn, kBMn, Epi, Pro>;
   // One bit per device: setting the attribute twice is harmless, so two threads racing here only repeat the call.
   static std::atomic<unsigned long long> attr_set{0ull};
   int dev = 0;
@@ -207,7 +210,7 @@ int launch_gemm_cfg(const void* a_ptr, long long lda, const void* b_ptr, long lo
   cudaLaunchConfig_t cfg;
   memset(&cfg, 0, sizeof(cfg));
   cfg.gridDim = dim3(static_cast<unsigned>(clusters * kCtaGroup), 1, 1);
-  cfg.blockDim = dim3(kNumThreads, 1, 1);
+  cfg.blockDim = dim3(kNumThreads + Pro::kWarps * 32, 1, 1);
   cfg.dynamicSmemBytes = Cfg::kSmemBytes;
   cfg.stream = stream;
   cudaLaunchAttribute attr[1];
@@ -219,7 +222,7 @@ int launch_gemm_cfg(const void* a_ptr, long long lda, const void* b_ptr, long lo
     cfg.attrs = attr;
     cfg.numAttrs = 1;
   }
-  cudaError_t e = cudaLaunchKernelEx(&cfg, kern, ta, tb, shape, ep, status);
+  cudaError_t e = cudaLaunchKernelEx(&cfg, kern, ta, tb, shape, ep, status, pp);
   if (e != cudaSuccess) return fail(kCudaError, std::string("GEMM launch failed: ") + cudaGetErrorString(e));
   return kOk;
 }

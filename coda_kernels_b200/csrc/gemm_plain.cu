@@ -86,3 +86,39 @@ extern "C" int coda_b200_gemm_sigmoid(const void* A, int64_t a_stride_m, int64_t
   return run_store<__nv_bfloat16, Act::kSigmoid>(A, a_stride_m, a_stride_k, B, b_stride_k, b_stride_n, nullptr, 0, 0, D, ldd, M, N,
                                                  K, nullptr, dev_status, stream);
 }
+
+extern "C" int coda_b200_gemm_dsigmoid_dgrad(const void* out, int64_t ld_out, const void* dout, int64_t ld_dout, const void* W,
+                                             int64_t ldw, void* G, int64_t ld_g, void* dx, int64_t ld_dx, int M, int N, int K,
+                                             int* dev_status, void* stream) {
+  // dx[M, K] = G[M, N] @ W[N, K] with G = dout * out * (1 - out) formed by the GEMM's own transform warps.
+  if (!out || !dout || !W || !G || !dx) return fail(kBadArgument, "NULL pointer");
+  if (M <= 0 || N <= 0 || K <= 0) return fail(kBadArgument, "extents must be positive");
+  if (dev_status == nullptr) return fail(kBadArgument, "device status word is required");
+  if (N % 8 || K % 8 || ld_out % 8 || ld_dout % 8 || ld_g % 8 || ld_dx % 8 || ldw % 8)
+    return fail(kBadArgument, "extents and leading dimensions must be multiples of 8");
+  if (ld_out < N || ld_dout < N || ld_g < N || ld_dx < K || ldw < K) return fail(kBadArgument, "a leading dimension is smaller than its row");
+  for (const void* p : {out, dout, W, static_cast<const void*>(G), static_cast<const void*>(dx)})
+    if ((reinterpret_cast<uintptr_t>(p) & 15u) != 0) return fail(kBadArgument, "pointers must be 16-byte aligned");
+  const LaunchOptions opt = launch_options();
+  if (opt.cta_group != 2) return fail(kBadArgument, "the fused sigmoid-gradient GEMM is built for CTA pairs only (cta_group = 2)");
+  using Epi = EpiStore<__nv_bfloat16, Act::kNone>;
+  Epi::Params ep;
+  ep.D = static_cast<__nv_bfloat16*>(dx);
+  ep.ldd = ld_dx;
+  ep.alpha = nullptr;
+  ep.C = nullptr;
+  ep.ldc = 0;
+  ep.c_is_fp32 = 0;
+  ep.use_tma = opt.epi_tma;
+  int rc = make_tmap_out(&ep.tm_d, ep.D, K, M, ld_dx);
+  if (rc != kOk) return rc;
+  ProDSigmoid::Params pp;
+  rc = make_tmap_bf16(&pp.tm_dout, dout, N, M, ld_dout, kBlockM);  // same geometry as the A operand (`out`)
+  if (rc != kOk) return rc;
+  pp.G = static_cast<__nv_bfloat16*>(G);
+  pp.ld_g = ld_g;
+  // A slot <- `out` [M, N] by TMA, rewritten in place; operand B = W[N, K] read MN-major (contiguous along the output
+  // dimension K); the contraction runs over N
+  return launch_gemm_cfg<2, 256, false, true, Epi, ProDSigmoid>(out, ld_out, W, ldw, M, /*N=*/K, /*K=*/N, ep, dev_status,
+                                                                static_cast<cudaStream_t>(stream), opt, pp);
+}

@@ -11,14 +11,19 @@ the two GEMMs of :func:`linear_backward`.
 
 from __future__ import annotations
 
+import os
 from typing import Optional
 
 import torch
 from torch import Tensor
 
 from .._guards import autocast_custom_bwd, autocast_custom_fwd, input_guard
-from ..ops import dsigmoid_backward, gemm_sigmoid
+from ..ops import dsigmoid_backward, gemm, gemm_dsigmoid_dgrad, gemm_sigmoid
 from ._common import linear_backward
+
+# CODA_B200_FUSED_DSIGMOID=1: form the sigmoid gradient inside the input-gradient GEMM (its A-operand prologue) instead
+# of in a separate element-wise pass.  Off by default: measured, the fused GEMM loses more than the pass costs.
+FUSED_DSIGMOID = os.environ.get("CODA_B200_FUSED_DSIGMOID", "0") == "1"
 
 
 class LinearSigmoid(torch.autograd.Function):
@@ -40,6 +45,10 @@ class LinearSigmoid(torch.autograd.Function):
     def backward(ctx, grad_out: Tensor):
         x, weight, result = ctx.saved_tensors
         need_dx, need_dw = ctx.needs_input_grad[:2]
+        if FUSED_DSIGMOID and need_dx and result.dtype == x.dtype:
+            dx, grad_pre = gemm_dsigmoid_dgrad(result, grad_out.to(dtype=x.dtype), weight)
+            dweight = gemm(grad_pre.mT, x) if need_dw else None
+            return dx, dweight, None
         grad_pre = dsigmoid_backward(result, grad_out.to(dtype=x.dtype))
         dx, dweight = linear_backward(grad_pre, x, weight, need_dx, need_dw)
         return dx, dweight, None

@@ -280,9 +280,23 @@ def _qknorm_rope_bwd_out(
     )
 
 
+@torch.library.custom_op("coda_b200::gemm_dsigmoid_dgrad_out", mutates_args=("grad_pre", "dx"), device_types="cuda")
+def _gemm_dsigmoid_dgrad_out(out: Tensor, dout: Tensor, weight: Tensor, grad_pre: Tensor, dx: Tensor) -> None:
+    M, N = out.shape
+    K = weight.shape[1]
+    check(
+        lib.coda_b200_gemm_dsigmoid_dgrad(
+            out.data_ptr(), out.stride(0), dout.data_ptr(), dout.stride(0), weight.data_ptr(), weight.stride(0),
+            grad_pre.data_ptr(), grad_pre.stride(0), dx.data_ptr(), dx.stride(0), M, N, K, status_word(out.device).data_ptr(),
+            _stream(out),
+        ),
+        "gemm_dsigmoid_dgrad",
+    )
+
+
 for _op in (
     _gemm_out, _gemm_sigmoid_out, _gemm_swiglu_out, _gemm_lse_out, _lse_finalize_out, _ce_grad_fixup, _gemm_qknorm_rope_out,
-    _dswiglu_out, _dsigmoid_out, _qknorm_rope_bwd_out,
+    _dswiglu_out, _dsigmoid_out, _qknorm_rope_bwd_out, _gemm_dsigmoid_dgrad_out,
 ):
     _op.register_fake(_noop_fake)
 
@@ -573,6 +587,19 @@ def dsigmoid_backward(out: Tensor, dout: Tensor) -> Tensor:
     grad_pre = torch.empty(dout.shape, dtype=_BF16, device=dout.device)
     _dsigmoid_out(out, dout, grad_pre)
     return grad_pre
+
+
+def gemm_dsigmoid_dgrad(out: Tensor, dout: Tensor, weight: Tensor) -> tuple[Tensor, Tensor]:
+    """``(dx, grad_pre)`` of ``out = sigmoid(x @ weight^T)``: ``grad_pre = dout * out * (1 - out)`` is formed inside the
+    input-gradient GEMM ``dx = grad_pre @ weight`` (by its transform warps, as the A operand) and written once for the
+    weight-gradient GEMM, instead of by a separate pass (coda/kernels/functional/sigmoid.py:33-38).  bf16 only."""
+    _require_cuda_bf16(out, dout, weight)
+    _require(out.shape == dout.shape and out.stride(1) == 1 and dout.stride(1) == 1 and weight.stride(1) == 1
+             and weight.shape[0] == out.shape[1], "gemm_dsigmoid_dgrad: out, dout [M, N] and weight [N, K] row-major expected")
+    grad_pre = torch.empty_like(out)
+    dx = torch.empty(out.shape[0], weight.shape[1], dtype=_BF16, device=out.device)
+    _gemm_dsigmoid_dgrad_out(out, dout, weight, grad_pre, dx)
+    return dx, grad_pre
 
 
 def qknorm_rope_bwd(

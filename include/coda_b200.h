@@ -77,6 +77,17 @@ int coda_b200_gemm_add(const void* A, int64_t a_stride_m, int64_t a_stride_k, co
                        int64_t b_stride_n, const void* C, int64_t ldc, int c_is_fp32, void* D, int64_t ldd, int d_is_fp32,
                        int M, int N, int K, const float* alpha, int* dev_status, void* stream);
 
+/* Input gradient of linear_sigmoid with the activation gradient fused into the
+ * GEMM's A-operand path: dx[M, K] = G[M, N] @ W[N, K] where G = dout * out *
+ * (1 - out) is formed tile by tile by the kernel's transform warps (packed bf16
+ * math) instead of being read from memory; G is also written once, for the
+ * weight-gradient GEMM.  out, dout, G: bf16 [M, N]; W: bf16 [N, K] row-major.
+ * Replaces the `sigmoid_backward` pass + dgrad GEMM of
+ * coda/kernels/functional/sigmoid.py:33-38 by one launch.  CTA-pair build only. */
+int coda_b200_gemm_dsigmoid_dgrad(const void* out, int64_t ld_out, const void* dout, int64_t ld_dout, const void* W, int64_t ldw,
+                                  void* G, int64_t ld_g, void* dx, int64_t ld_dx, int M, int N, int K, int* dev_status,
+                                  void* stream);
+
 /* D = sigmoid(A @ B).  For N <= 64 (one gate per attention head, the shape
  * the reference benchmarks) a 64-column tile is used.  Replaces `coda::_gemm_sigmoid_epi`
  * (coda/core/gemm/functional.py:199-217; epilogue coda/core/gemm/epilogues.py:39-41). */

@@ -492,3 +492,27 @@ def test_skinny_sigmoid_uses_the_64_column_tile(ck, n_gates, cta_group):
     close(out32, ro, tol=1e-4, what="out fp32")
     close(dx, grads["x"], what="dx")
     close(dw, grads["weight"], what="dweight")
+
+
+@pytest.mark.parametrize("shape", [(520, 328, 264), (1000, 520, 1032), (4096, 512, 2048)])
+def test_fused_sigmoid_gradient_dgrad(ck, shape):
+    """``dx`` and ``grad_pre`` from the input-gradient GEMM whose transform warps form ``dout * out * (1 - out)`` as its
+    A operand, against the separate pass + plain GEMM and against the oracle (ragged rows, columns and contraction)."""
+    M, K, N = shape
+    d = inputs.sigmoid_inputs(M, K, N)
+    x, w, dout = d["x"].to(DEV), d["weight"].to(DEV), d["dout"].to(DEV)
+    out = ck.ops.gemm_sigmoid(x, w.mT)
+    dx, g = ck.ops.gemm_dsigmoid_dgrad(out, dout, w)
+    g_ref = ck.ops.dsigmoid_backward(out, dout)
+    dx_ref = ck.ops.gemm(g_ref, w)
+    status_ok(ck)
+    # the fused kernel forms grad_pre in packed bf16 (three roundings), the separate pass in fp32 (one): they agree to a
+    # few bf16 ulps, and both sit within the gradient tolerance of the exact value
+    assert eager.max_rel_err(g, g_ref.float()) <= 1e-2
+    assert eager.max_rel_err(dx, dx_ref.float()) <= 1e-2
+    exact_g = dout.float() * out.float() * (1.0 - out.float())
+    close(g, exact_g, what="dgrad_pre")
+    (ro,), grads = eager.fwd_bwd(eager.linear_sigmoid, {"x": x, "weight": w}, ["x", "weight"], dout)
+    close(dx, grads["x"], what="dx")
+    dw = ck.ops.gemm(g.mT, x)
+    close(dw, grads["weight"], what="dweight")
