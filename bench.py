@@ -66,9 +66,9 @@ SHAPES = {
 
 
 # DRAM bytes per launch of the dominant kernel (dram__bytes_read.sum + dram__bytes_write.sum from one ncu capture).
-# swiglu: 866.9 MB measured at 4096 rows (the committed ncu summary of the swiglu GEMMs), x4 for the 16384-row launch,
+# swiglu: 893.4 MB (561.5 read + 331.9 written) measured at 4096 rows (the committed ncu summary of the swiglu GEMMs), x4 for the 16384-row launch,
 # since the traffic grows in proportion to the rows.
-NCU_TRAFFIC = {"swiglu": 3.467e9}
+NCU_TRAFFIC = {"swiglu": 3.574e9}
 
 
 def algorithmic_flops(op: str, s: dict) -> float:

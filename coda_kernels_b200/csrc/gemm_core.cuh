@@ -460,8 +460,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
     tmem_dealloc<kCtaGroup>(tmem_base, Cfg::kTmemCols);
   }
   if (threadIdx.x == 0) {
-    const int code = *abort_word;
-    if (code != 0) atomicMax(status, code);
+    report_status(status, *abort_word);
   }
 }
 

@@ -25,6 +25,18 @@ enum : int {
 
 constexpr unsigned long long kWaitTimeoutNs = 2000000000ull;  // 2 s
 
+// Records a failure code in the status word.  The word may live in device memory or in pinned host memory that the
+// device maps (then the host sees the code with a plain read, no copy), so this is a system-scope store rather than an
+// atomic.  Any non-zero value reports the failure; a CTA that merely follows its peer does not overwrite a code that
+// names the wait which really expired.
+__device__ __forceinline__ void report_status(int* status, int code) {
+  if (code == 0) return;
+  volatile int* word = status;
+  if (code == kErrPeerAbort && *word != 0) return;
+  *word = code;
+  __threadfence_system();
+}
+
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
 }

@@ -23,7 +23,7 @@ __global__ void wait_timeout_kernel(int* __restrict__ status, unsigned long long
   const bool ok = mbar_wait_for(bar, 0u, &abort_word, kErrTimeoutFull, timeout_ns);
   __syncthreads();
   if (threadIdx.x == 0) {
-    if (!ok || abort_word != 0) atomicMax(status, abort_word != 0 ? abort_word : static_cast<int>(kErrTimeoutFull));
+    if (!ok || abort_word != 0) report_status(status, abort_word != 0 ? abort_word : static_cast<int>(kErrTimeoutFull));
     if (waited_us != nullptr) *waited_us = static_cast<int>((globaltimer_ns() - t0) / 1000ull);
   }
 }

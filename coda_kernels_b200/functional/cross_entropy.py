@@ -5,16 +5,15 @@ Drop-in for coda/kernels/functional/cross_entropy.py:97-193 (signatures, default
 Dataflow here: the forward GEMM's epilogue keeps a row max / sum-exp per column tile and stores only unnormalised
 probabilities; a per-row reduction gives the log-sum-exp and the row losses; one in-place pass turns the stored
 probabilities into ``softmax - onehot`` (exactly zero for ignored rows).  That buffer is the only ``[M, V]`` tensor
-and is what the node saves.  The backward is :func:`linear_backward` over it with ``alpha = dloss / count`` read from
-device memory, so neither direction synchronises with the host.  ``fused_lse`` is accepted for signature parity; both
+and is what the node saves.  The backward is :func:`coda_kernels_b200.ops.linear_backward` over it with
+``alpha = dloss / count`` read from device memory, so neither direction synchronises with the host.  ``fused_lse`` is accepted for signature parity; both
 values run this path.
 """
 
 import torch
 
 from .._guards import autocast_custom_bwd, autocast_custom_fwd, input_guard
-from ..ops import gemm_lse_dlogits, gemm_lse_select_logits
-from ._common import linear_backward, masked_loss
+from ..ops import cross_entropy_backward, cross_entropy_forward
 
 
 class LinearCrossEntropy(torch.autograd.Function):
@@ -24,8 +23,7 @@ class LinearCrossEntropy(torch.autograd.Function):
     @input_guard
     @autocast_custom_fwd
     def forward(ctx, x, weight, target, ignore_index: int, reduction: str, fused_lse: bool) -> torch.Tensor:
-        row_losses, dlogits = gemm_lse_dlogits(x, weight.mT, target, ignore_index)
-        loss, inv_count = masked_loss(row_losses, target, ignore_index, reduction)
+        loss, inv_count, dlogits = cross_entropy_forward(x, weight, target, ignore_index, reduction, store_grad=True)
         ctx.save_for_backward(x, weight, dlogits, inv_count)
         return loss
 
@@ -34,9 +32,8 @@ class LinearCrossEntropy(torch.autograd.Function):
     @autocast_custom_bwd
     def backward(ctx, dloss: torch.Tensor):
         x, weight, dlogits, inv_count = ctx.saved_tensors
-        alpha = (dloss if inv_count is None else dloss * inv_count).reshape(1).to(dtype=torch.float32)
         need_dx, need_dw = ctx.needs_input_grad[:2]
-        return (*linear_backward(dlogits, x, weight, need_dx, need_dw, alpha=alpha), None, None, None, None)
+        return (*cross_entropy_backward(dloss, inv_count, dlogits, x, weight, need_dx, need_dw), None, None, None, None)
 
 
 def linear_cross_entropy(
@@ -54,8 +51,7 @@ def linear_cross_entropy(
 
 @input_guard
 def _forward_only(x, weight, target, ignore_index: int, reduction: str) -> torch.Tensor:
-    row_losses, _, _ = gemm_lse_select_logits(x, weight.mT, target, ignore_index)
-    return masked_loss(row_losses, target, ignore_index, reduction)[0]
+    return cross_entropy_forward(x, weight, target, ignore_index, reduction, store_grad=False)[0]
 
 
 def linear_cross_entropy_forward(

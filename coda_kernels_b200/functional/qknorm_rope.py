@@ -20,8 +20,7 @@ import torch
 from torch import Tensor
 
 from .._guards import autocast_custom_bwd, autocast_custom_fwd, input_guard
-from ..ops import gemm_qknorm_rope, qknorm_rope_bwd
-from ._common import linear_backward
+from ..ops import qknorm_rope_backward, qknorm_rope_forward
 
 
 class LinearQKNormRope(torch.autograd.Function):
@@ -32,10 +31,8 @@ class LinearQKNormRope(torch.autograd.Function):
     @autocast_custom_fwd
     def forward(ctx, x: Tensor, weight: Tensor, gamma: Tensor, positions: Tensor, frequencies: Tensor, head_dim: int,
                 num_heads_q: int, num_heads_k: int, eps: float):
-        rotated, preact, head_mean_sq, v = gemm_qknorm_rope(
-            x, weight.mT, gamma, positions, frequencies, head_dim, num_heads_q, num_heads_k, eps)
-        if v is None:  # a weight without v rows
-            v = x.new_empty(x.shape[0], 0)
+        rotated, preact, head_mean_sq, v = qknorm_rope_forward(
+            x, weight, gamma, positions, frequencies, head_dim, num_heads_q, num_heads_k, eps)  # v: zero columns without v rows
         ctx.head_dim, ctx.num_heads_q, ctx.num_heads_k, ctx.eps = head_dim, num_heads_q, num_heads_k, eps
         ctx.save_for_backward(x, weight, gamma, positions, frequencies, preact, head_mean_sq)
         width_q = head_dim * num_heads_q
@@ -50,11 +47,9 @@ class LinearQKNormRope(torch.autograd.Function):
     def backward(ctx, grad_q: Tensor, grad_k: Tensor, grad_v: Tensor):
         x, weight, gamma, positions, frequencies, preact, head_mean_sq = ctx.saved_tensors
         head_dim, num_heads_q, num_heads_k, eps = ctx.head_dim, ctx.num_heads_q, ctx.num_heads_k, ctx.eps
-        has_v = grad_v.shape[1] > 0
-        grad_all, dgamma = qknorm_rope_bwd(grad_q, grad_k, grad_v if has_v else None, preact, head_mean_sq, gamma, positions,
-                                           frequencies, head_dim, num_heads_q, num_heads_k, eps)
-        dx, dweight = linear_backward(grad_all, x, weight, ctx.needs_input_grad[0], ctx.needs_input_grad[1])
-        return (dx, dweight, dgamma.to(dtype=gamma.dtype)) + (None,) * 6
+        dx, dweight, dgamma = qknorm_rope_backward(grad_q, grad_k, grad_v, x, weight, preact, head_mean_sq, gamma, positions, frequencies,
+                                                   head_dim, num_heads_q, num_heads_k, eps, ctx.needs_input_grad[0], ctx.needs_input_grad[1])
+        return (dx, dweight, dgamma) + (None,) * 6
 
 
 def linear_qknorm_rope(x: Tensor, weight: Tensor, gamma: Tensor, positions: Tensor, frequencies: Tensor, head_dim: int,

@@ -6,7 +6,7 @@ reference does, and returns ``None`` for ``out_dtype``.
 
 Forward is one launch (GEMM with the sigmoid in its epilogue; a 128-column tile is picked automatically when ``weight``
 has few rows, e.g. one gate per attention head).  Backward is one HBM-bound pass ``dout * out * (1 - out)`` followed by
-the two GEMMs of :func:`linear_backward`.
+the two GEMMs of :func:`coda_kernels_b200.ops.linear_backward`.
 """
 
 from __future__ import annotations
@@ -18,8 +18,7 @@ import torch
 from torch import Tensor
 
 from .._guards import autocast_custom_bwd, autocast_custom_fwd, input_guard
-from ..ops import dsigmoid_backward, gemm, gemm_dsigmoid_dgrad, gemm_sigmoid
-from ._common import linear_backward
+from ..ops import gemm, gemm_dsigmoid_dgrad, sigmoid_backward, sigmoid_forward
 
 # CODA_B200_FUSED_DSIGMOID=1: form the sigmoid gradient inside the input-gradient GEMM (its A-operand prologue) instead
 # of in a separate element-wise pass.  Off by default: measured, the fused GEMM loses more than the pass costs.
@@ -33,9 +32,7 @@ class LinearSigmoid(torch.autograd.Function):
     @input_guard
     @autocast_custom_fwd
     def forward(ctx, x: Tensor, weight: Tensor, out_dtype: Optional[torch.dtype]) -> Tensor:
-        rows, features = x.shape[0], weight.shape[0]
-        result = x.new_empty((rows, features), dtype=x.dtype if out_dtype is None else out_dtype)
-        gemm_sigmoid(x, weight.mT, out=result)
+        result = sigmoid_forward(x, weight, out_dtype)
         ctx.save_for_backward(x, weight, result)
         return result
 
@@ -49,8 +46,7 @@ class LinearSigmoid(torch.autograd.Function):
             dx, grad_pre = gemm_dsigmoid_dgrad(result, grad_out.to(dtype=x.dtype), weight)
             dweight = gemm(grad_pre.mT, x) if need_dw else None
             return dx, dweight, None
-        grad_pre = dsigmoid_backward(result, grad_out.to(dtype=x.dtype))
-        dx, dweight = linear_backward(grad_pre, x, weight, need_dx, need_dw)
+        dx, dweight = sigmoid_backward(result, grad_out, x, weight, need_dx, need_dw)
         return dx, dweight, None
 
 

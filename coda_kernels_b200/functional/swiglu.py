@@ -6,7 +6,7 @@ shape ``[2F, K]`` whose even rows are the gate projection and whose odd rows are
 Forward is ONE kernel launch: the tcgen05 GEMM whose epilogue reads each (gate, up) pair from adjacent accumulator
 columns of one thread, writes the bf16 pre-activation (kept for the backward) and the activated product.  Backward is
 one HBM-bound pass that turns (pre-activation, dout) into the pre-activation gradient, then the two GEMMs of
-:func:`linear_backward`.
+:func:`coda_kernels_b200.ops.linear_backward`.  Each direction is one call into the compiled dispatch layer.
 """
 
 from __future__ import annotations
@@ -15,8 +15,7 @@ import torch
 from torch import Tensor
 
 from .._guards import autocast_custom_bwd, autocast_custom_fwd, input_guard
-from ..ops import dswiglu_backward, gemm_swiglu
-from ._common import linear_backward
+from ..ops import swiglu_backward, swiglu_forward
 
 
 class LinearSwiGLU(torch.autograd.Function):
@@ -26,8 +25,7 @@ class LinearSwiGLU(torch.autograd.Function):
     @input_guard
     @autocast_custom_fwd
     def forward(ctx, x: Tensor, weight: Tensor) -> Tensor:
-        # weight.mT is a view: the kernel consumes the [2F, K] rows as a K-major B operand
-        saved_preact, activated = gemm_swiglu(x, weight.mT)
+        saved_preact, activated = swiglu_forward(x, weight)
         ctx.save_for_backward(x, weight, saved_preact)
         return activated
 
@@ -37,7 +35,7 @@ class LinearSwiGLU(torch.autograd.Function):
     def backward(ctx, grad_out: Tensor):
         x, weight, saved_preact = ctx.saved_tensors
         need_dx, need_dw = ctx.needs_input_grad[:2]
-        return linear_backward(dswiglu_backward(saved_preact, grad_out), x, weight, need_dx, need_dw)
+        return swiglu_backward(saved_preact, grad_out, x, weight, need_dx, need_dw)
 
 
 def linear_swiglu(x: Tensor, weight: Tensor) -> Tensor:

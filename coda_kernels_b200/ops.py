@@ -11,6 +11,7 @@ memory and the current stream; all arithmetic runs in the library's kernels.
 
 from __future__ import annotations
 
+import ctypes
 import os
 from typing import Optional
 
@@ -22,74 +23,58 @@ from ._lib import check, lib
 
 _BF16 = torch.bfloat16
 _status_words: dict[int, Tensor] = {}
+_status_views: dict[int, ctypes.c_int] = {}
 
 
 def status_word(device: torch.device) -> Tensor:
-    """Per-device int32 word that kernels set when a bounded wait expires."""
+    """Per-device int32 word that kernels set when a bounded wait expires.
+
+    It lives in pinned host memory, which the device maps at the same address: a kernel writes it only on its failure
+    path (one store over PCIe), and the host sees the code by reading the word, without a copy, a stream operation or
+    any CUDA call.  That is what makes the check cheap enough to run in every operator call."""
     idx = device.index if device.index is not None else torch.cuda.current_device()
     word = _status_words.get(idx)
     if word is None:
-        word = torch.zeros(1, dtype=torch.int32, device=torch.device("cuda", idx))
+        with torch.cuda.device(idx):
+            word = torch.zeros(1, dtype=torch.int32).pin_memory()
         _status_words[idx] = word
+        _status_views[idx] = ctypes.c_int.from_address(word.data_ptr())
     return word
 
 
 def check_device_status(device: Optional[torch.device] = None) -> None:
-    """Synchronously read the status word; raise if any kernel reported trouble."""
+    """Wait for the device, then read the status word; raise if any kernel reported trouble."""
     device = device if device is not None else torch.device("cuda", torch.cuda.current_device())
-    code = int(status_word(device).item())
+    word = status_word(device)
+    torch.cuda.synchronize(device)
+    code = int(word.item())
     if code != 0:
-        status_word(device).zero_()
+        word.zero_()
         raise RuntimeError(f"coda_b200 kernel reported device-side error code {code} (a bounded wait expired)")
-
-
-class _StatusSnapshot:
-    """Pinned host copy of one device's status word plus the event that says when the copy has landed."""
-
-    def __init__(self, device: torch.device):
-        self.host = torch.zeros(1, dtype=torch.int32).pin_memory()
-        self.event = torch.cuda.Event()
-        self.pending = False
-        self.device = device
-
-
-_snapshots: dict[int, _StatusSnapshot] = {}
 
 
 def lazy_status_check(device: Optional[torch.device] = None) -> None:
     """Report an expired device-side wait without synchronising.
 
-    Called at the start of every operator's forward and backward.  It first looks at the previous snapshot of the
-    status word: if that 4-byte copy has landed (an event query, no wait) and the word is non-zero, it raises.  Then it
-    enqueues a fresh asynchronous copy of the word to pinned host memory on the current stream.  So a kernel that gave
-    up is reported by the next operator call that runs after its launch has finished, typically the backward of the
-    same step, instead of yielding silent garbage for the rest of a training run.  Nothing is done while a CUDA graph
-    is being captured or while ``torch.compile`` traces the caller.
+    Called at the start of every operator's forward and backward: a plain read of the status word in pinned host
+    memory.  A kernel that gave up is therefore reported by the first operator call after its launch has finished,
+    typically the backward of the same step, instead of yielding silent garbage for the rest of a training run.  It
+    costs no CUDA call and enqueues nothing, so it also runs while a CUDA graph is being captured; it is skipped
+    while ``torch.compile`` traces the caller.
     """
     if torch.compiler.is_compiling():
         return
-    if device is None:
-        device = torch.device("cuda", torch.cuda.current_device())
-    idx = device.index if device.index is not None else torch.cuda.current_device()
-    if torch.cuda.is_current_stream_capturing():
-        return
-    snap = _snapshots.get(idx)
-    if snap is None:
-        snap = _snapshots[idx] = _StatusSnapshot(torch.device("cuda", idx))
-    if snap.pending:
-        if not snap.event.query():
-            return  # the previous copy is still behind queued work: look again at the next call
-        snap.pending = False
-        code = int(snap.host[0])
-        if code != 0:
-            status_word(snap.device).zero_()
-            snap.host.zero_()
-            raise RuntimeError(
-                f"coda_b200: a kernel on cuda:{idx} reported device-side error code {code} (a bounded wait expired); "
-                "the outputs of that launch are incomplete")
-    snap.host.copy_(status_word(snap.device), non_blocking=True)
-    snap.event.record()
-    snap.pending = True
+    idx = torch.cuda.current_device() if device is None or device.index is None else device.index
+    view = _status_views.get(idx)
+    if view is None:
+        status_word(torch.device("cuda", idx))
+        view = _status_views[idx]
+    code = view.value
+    if code != 0:
+        view.value = 0
+        raise RuntimeError(
+            f"coda_b200: a kernel on cuda:{idx} reported device-side error code {code} (a bounded wait expired); "
+            "the outputs of that launch are incomplete")
 
 
 def _sync_status_hook(what: str) -> None:
@@ -306,6 +291,7 @@ for _op in (
 # TORCH_LIBRARY shim over the same C ABI that skips the per-launch Python work of the ctypes ops above.  Eager calls
 # go through it; while ``torch.compile`` traces, the Python custom ops above are used (opaque to the tracer, and
 # dispatch cost is irrelevant there).  ``CODA_B200_DISPATCH=ctypes`` keeps every call on the ctypes binding.
+# The same library also holds one entry point per direction of each operator (see "whole operators" at the end).
 _native = None
 if os.environ.get("CODA_B200_DISPATCH", "native") != "ctypes":
     if not _lib_module.NATIVE_LIB_PATH.exists():
@@ -330,7 +316,7 @@ if os.environ.get("CODA_B200_DISPATCH", "native") != "ctypes":
 
             def call(*args):
                 try:
-                    op(*args)
+                    return op(*args)
                 except RuntimeError as ex:
                     raise _lib_module.CodaB200Error(str(ex).split("\n")[0]) from None
 
@@ -338,7 +324,6 @@ if os.environ.get("CODA_B200_DISPATCH", "native") != "ctypes":
             return call
 
     _native = _Native()
-
     _ct_gemm_out, _ct_gemm_sigmoid_out, _ct_gemm_swiglu_out, _ct_gemm_lse_out = _gemm_out, _gemm_sigmoid_out, _gemm_swiglu_out, _gemm_lse_out
     _ct_lse_finalize_out, _ct_ce_grad_fixup, _ct_gemm_qknorm_rope_out = _lse_finalize_out, _ce_grad_fixup, _gemm_qknorm_rope_out
     _ct_dswiglu_out, _ct_dsigmoid_out, _ct_qknorm_rope_bwd_out = _dswiglu_out, _dsigmoid_out, _qknorm_rope_bwd_out
@@ -622,3 +607,116 @@ def qknorm_rope_bwd(
         num_heads_k, float(eps), grad, dgamma, scratch,
     )
     return grad, dgamma
+
+
+# ------------------------------------------------------------------------------------------------ whole operators
+# One call per direction of an autograd node.  Eagerly they are single entry points of the compiled dispatch layer
+# (outputs allocated and every launch of that direction issued from C++); while ``torch.compile`` traces, or with
+# ``CODA_B200_DISPATCH=ctypes``, the same sequence is composed from the wrappers above.
+
+
+# CODA_B200_DISPATCH=launch keeps the compiled per-launch ops but composes each operator in Python (what the tests
+# compare the whole-operator entry points against).
+_WHOLE_OPERATORS = os.environ.get("CODA_B200_DISPATCH", "native") == "native"
+
+
+def _fast() -> bool:
+    return _WHOLE_OPERATORS and _native is not None and not torch.compiler.is_compiling()
+
+
+def linear_backward(grad_pre: Tensor, x: Tensor, weight: Tensor, need_dx: bool = True, need_dw: bool = True,
+                    alpha: Optional[Tensor] = None) -> tuple[Optional[Tensor], Optional[Tensor]]:
+    """Gradients of ``pre = x @ weight^T`` given ``grad_pre = dL/dpre`` (times the device scalar ``alpha``, if given).
+
+    ``dx = grad_pre @ weight`` reads the ``[N, K]`` weight as an MN-major B operand and ``dweight = grad_pre^T @ x``
+    reads both operands MN-major, so neither needs a transposed copy.  ``alpha`` is applied in the GEMM epilogues (read
+    from device memory: no host synchronisation).
+    """
+    if _fast():
+        return _native.linear_backward(grad_pre, x, weight, need_dx, need_dw, alpha, status_word(x.device))
+    dx = gemm(grad_pre, weight, alpha=alpha) if need_dx else None
+    dweight = gemm(grad_pre.mT, x, alpha=alpha) if need_dw else None
+    return dx, dweight
+
+
+def swiglu_forward(x: Tensor, weight: Tensor) -> tuple[Tensor, Tensor]:
+    """``(preact, postact)`` of ``x @ weight^T`` with interleaved gate/up rows in ``weight [2F, K]``."""
+    _require_cuda_bf16(x, weight)
+    if _fast():
+        return _native.swiglu_fwd(x, weight, status_word(x.device))
+    return gemm_swiglu(x, weight.mT)  # weight.mT is a view: the kernel consumes the [2F, K] rows as a K-major B operand
+
+
+def swiglu_backward(preact: Tensor, dout: Tensor, x: Tensor, weight: Tensor, need_dx: bool, need_dw: bool):
+    if _fast():
+        return _native.swiglu_bwd(preact, dout, x, weight, need_dx, need_dw, status_word(x.device))
+    return linear_backward(dswiglu_backward(preact, dout), x, weight, need_dx, need_dw)
+
+
+def sigmoid_forward(x: Tensor, weight: Tensor, out_dtype: Optional[torch.dtype]) -> Tensor:
+    _require_cuda_bf16(x, weight)
+    out_dtype = x.dtype if out_dtype is None else out_dtype
+    _require(out_dtype in (_BF16, torch.float32), "gemm_sigmoid: out must be bfloat16 or float32")
+    if _fast():
+        return _native.sigmoid_fwd(x, weight, out_dtype == torch.float32, status_word(x.device))
+    return gemm_sigmoid(x, weight.mT, out=x.new_empty((x.shape[0], weight.shape[0]), dtype=out_dtype))
+
+
+def sigmoid_backward(out: Tensor, dout: Tensor, x: Tensor, weight: Tensor, need_dx: bool, need_dw: bool):
+    dout = dout.to(dtype=x.dtype)
+    if _fast():
+        return _native.sigmoid_bwd(out, dout, x, weight, need_dx, need_dw, status_word(x.device))
+    return linear_backward(dsigmoid_backward(out, dout), x, weight, need_dx, need_dw)
+
+
+def cross_entropy_forward(x: Tensor, weight: Tensor, target: Tensor, ignore_index: int, reduction: str,
+                          store_grad: bool) -> tuple[Tensor, Optional[Tensor], Optional[Tensor]]:
+    """``(loss, inv_count, dlogits)``.  ``inv_count`` (0-d device tensor, ``"mean"`` only) is one over the number of rows
+    whose target is not ``ignore_index``; ignored rows carry an exact zero loss.  ``dlogits`` (with ``store_grad``) is
+    the bf16 gradient of the SUM of the row losses w.r.t. the logits: the only ``[M, V]`` buffer of the operator."""
+    _require_cuda_bf16(x, weight)
+    _debug_check_targets(target, weight.shape[0], ignore_index)
+    if _fast():
+        return _native.cross_entropy_fwd(x, weight, target, int(ignore_index), reduction == "mean", store_grad, status_word(x.device))
+    if store_grad:
+        row_losses, dlogits = gemm_lse_dlogits(x, weight.mT, target, ignore_index)
+    else:
+        row_losses, dlogits = gemm_lse_select_logits(x, weight.mT, target, ignore_index)[0], None
+    total = row_losses.sum()
+    if reduction == "sum":
+        return total, None, dlogits
+    inv_count = (target != ignore_index).sum().float().reciprocal()
+    return total * inv_count, inv_count, dlogits
+
+
+def cross_entropy_backward(dloss: Tensor, inv_count: Optional[Tensor], dlogits: Tensor, x: Tensor, weight: Tensor, need_dx: bool,
+                           need_dw: bool):
+    if _fast():
+        return _native.cross_entropy_bwd(dloss, inv_count, dlogits, x, weight, need_dx, need_dw, status_word(x.device))
+    alpha = (dloss if inv_count is None else dloss * inv_count).reshape(1).to(dtype=torch.float32)
+    return linear_backward(dlogits, x, weight, need_dx, need_dw, alpha=alpha)
+
+
+def qknorm_rope_forward(x: Tensor, weight: Tensor, gamma: Tensor, positions: Tensor, frequencies: Tensor, head_dim: int,
+                        num_heads_q: int, num_heads_k: int, eps: float) -> tuple[Tensor, Tensor, Tensor, Tensor]:
+    """``(qk, preact, head_mean_sq, v)`` from ONE GEMM over the whole ``[(hq + hk + hv) * d, K]`` weight; ``v`` has zero
+    columns when the weight has no v rows."""
+    _require_cuda_bf16(x, weight, gamma)
+    if _fast():
+        return _native.qknorm_rope_fwd(x, weight, gamma, positions, frequencies, head_dim, num_heads_q, num_heads_k, float(eps),
+                                       status_word(x.device))
+    qk, preact, mean_sq, v = gemm_qknorm_rope(x, weight.mT, gamma, positions, frequencies, head_dim, num_heads_q, num_heads_k, eps)
+    return qk, preact, mean_sq, (x.new_empty(x.shape[0], 0) if v is None else v)
+
+
+def qknorm_rope_backward(dq: Tensor, dk: Tensor, dv: Tensor, x: Tensor, weight: Tensor, preact: Tensor, head_mean_sq: Tensor,
+                         gamma: Tensor, positions: Tensor, frequencies: Tensor, head_dim: int, num_heads_q: int, num_heads_k: int,
+                         eps: float, need_dx: bool, need_dw: bool):
+    """``(dx, dweight, dgamma)``; ``dv`` with zero columns stands for "no v rows"."""
+    if _fast():
+        return _native.qknorm_rope_bwd(dq, dk, dv, x, weight, preact, head_mean_sq, gamma, positions, frequencies, head_dim, num_heads_q,
+                                       num_heads_k, float(eps), need_dx, need_dw, status_word(x.device))
+    grad_all, dgamma = qknorm_rope_bwd(dq, dk, dv if dv.shape[1] > 0 else None, preact, head_mean_sq, gamma, positions, frequencies,
+                                       head_dim, num_heads_q, num_heads_k, eps)
+    dx, dweight = linear_backward(grad_all, x, weight, need_dx, need_dw)
+    return dx, dweight, dgamma.to(dtype=gamma.dtype)

@@ -4,7 +4,7 @@
  *
  * Conventions
  *  - Every pointer is a device pointer unless stated otherwise; the library
- *    allocates nothing and never synchronises the device.  Work is enqueued on
+ *    allocates no device memory and never synchronises the device.  Work is enqueued on
  *    `stream` (a cudaStream_t passed as void*; NULL = legacy default stream) of
  *    the current device.
  *  - Matrices are bf16 unless stated otherwise.  An operand is described by its
@@ -14,8 +14,12 @@
  *  - Functions return 0 on success or a negative code (CODA_B200_E*) for
  *    arguments rejected on the host; coda_b200_last_error() then describes the
  *    problem.  Device-side trouble (a bounded wait that expired) is reported
- *    asynchronously through `dev_status`, a device int32 that stays 0 on
- *    success and receives a positive code otherwise.
+ *    asynchronously through `dev_status`, an int32 the device can write that
+ *    stays 0 on success and receives a positive code otherwise.  It may be
+ *    device memory (read it back, or use coda_b200_status_poll) or pinned host
+ *    memory, which the device maps at the same address: the kernels write it
+ *    with a plain system-scope store, only on the failure path, and the host
+ *    then sees the code by reading the word, with no copy and no CUDA call.
  *
  * Each entry point names the reference interface it stands in for, as
  * file:line inside the coda-kernels project.
@@ -60,6 +64,16 @@ int coda_b200_set_option(const char* name, int value);
  * the kernel returns normally and dev_status receives a positive code.
  * waited_us (device int32, may be NULL) receives the time the wait took. */
 int coda_b200_selftest_wait_timeout(int* dev_status, int64_t timeout_us, int* waited_us, void* stream);
+
+/* Non-blocking look at a `dev_status` that lives in device memory (no counterpart in the reference; a status word in
+ * pinned host memory needs no call at all).  Each call first checks the snapshot the
+ * previous call took: if that 4-byte copy has landed (an event query, never a wait) and holds a code, the code
+ * (> 0) is returned once and the device word is cleared by an asynchronous memset on `stream`.  Otherwise it enqueues a
+ * fresh copy of the word into pinned host memory on `stream` and returns 0.  So the call after the one that follows a
+ * failed launch's completion reports it.  Returns 0 without enqueuing anything while `stream` is capturing; negative on
+ * a CUDA error.  The one piece of state the library owns: a pinned host word and an event per device, created by
+ * the first poll on that device. */
+int coda_b200_status_poll(int* dev_status, void* stream);
 
 /* D[M,N] = alpha * (A[M,K] @ B[K,N]); D row-major with leading dimension ldd,
  * bf16 (d_is_fp32 = 0) or fp32 (1); alpha = device fp32 scalar or NULL.

@@ -63,3 +63,56 @@ def test_dispatch_cost_of_the_shim_is_below_the_ctypes_ops():
     native, ct = per_call(ops._gemm_out), per_call(ops._ct_gemm_out)
     print(f"host time per launch: compiled shim {native * 1e6:.1f} us, ctypes custom op {ct * 1e6:.1f} us")
     assert native < ct
+
+
+def test_whole_operator_entry_points_match_the_composed_path(monkeypatch):
+    """Forward and backward of the four operators through the one-call-per-direction entry points of the compiled layer
+    against the same launches composed in Python: the same kernels on the same inputs, so the same bits."""
+    import coda_kernels_b200 as ck
+    from coda_kernels_b200 import ops
+
+    dev = torch.device(DEV)
+
+    def leaf(t):
+        return t.to(dev).detach().requires_grad_(True)
+
+    def swiglu():
+        d = inputs.swiglu_inputs(333, 264, 136)
+        x, w = leaf(d["x"]), leaf(d["weight"])
+        y = ck.linear_swiglu(x, w)
+        y.backward(d["dout"].to(dev))
+        return y, x.grad, w.grad
+
+    def sigmoid(out_dtype=None):
+        d = inputs.sigmoid_inputs(300, 136, 72)
+        x, w = leaf(d["x"]), leaf(d["weight"])
+        y = ck.linear_sigmoid(x, w, out_dtype)
+        y.backward(d["dout"].to(dev).to(y.dtype))
+        return y, x.grad, w.grad
+
+    def cross_entropy(reduction):
+        d = inputs.cross_entropy_inputs(257, 136, 1000)
+        x, w = leaf(d["x"]), leaf(d["weight"])
+        loss = ck.linear_cross_entropy(x, w, d["target"].to(dev), reduction=reduction)
+        (loss * 3.0).backward()
+        only = ck.linear_cross_entropy_forward(x.detach(), w.detach(), d["target"].to(dev), reduction=reduction)
+        return loss, only, x.grad, w.grad
+
+    def qknorm(hv):
+        d = inputs.qknorm_rope_inputs(200, 136, 128, 4, 2, hv, 64)
+        x, w, g = leaf(d["x"]), leaf(d["weight"]), leaf(d["gamma"])
+        q, k, v = ck.linear_qknorm_rope(x, w, g, d["positions"].to(dev), d["frequencies"].to(dev), 128, 4, 2, 1e-6)
+        torch.autograd.backward((q, k, v), (d["dq"].to(dev), d["dk"].to(dev), d["dv"].to(dev)))
+        return q, k, v, x.grad, w.grad, g.grad
+
+    cases = [swiglu, sigmoid, lambda: sigmoid(torch.float32), lambda: cross_entropy("mean"), lambda: cross_entropy("sum"),
+             lambda: qknorm(2), lambda: qknorm(0)]
+    assert ops._fast(), "eager calls should use the whole-operator entry points by default"
+    whole = [case() for case in cases]
+    monkeypatch.setattr(ops, "_WHOLE_OPERATORS", False)
+    composed = [case() for case in cases]
+    torch.cuda.synchronize()
+    ops.check_device_status(dev)
+    for a, b in zip(whole, composed):
+        for u, v in zip(a, b):
+            assert u.dtype == v.dtype and u.shape == v.shape and torch.equal(u, v)

@@ -41,7 +41,8 @@ def test_bounded_wait_expires_and_reports():
 
 def test_operator_path_reports_an_expired_wait_without_sync():
     """A kernel that gave up is reported by a later operator call on its own (no explicit status read, no
-    CODA_B200_SYNC_STATUS): the guards look at an asynchronous snapshot of the status word."""
+    CODA_B200_SYNC_STATUS): the status word sits in pinned host memory, the failing kernel writes it there, and the
+    guards read it as plain memory."""
     import coda_kernels_b200 as ck
     from coda_kernels_b200 import _lib, ops
 
@@ -56,7 +57,7 @@ def test_operator_path_reports_an_expired_wait_without_sync():
     rc = _lib.lib.coda_b200_selftest_wait_timeout(word.data_ptr(), 2000, None, torch.cuda.current_stream().cuda_stream)
     assert rc == 0
     with pytest.raises(RuntimeError, match="device-side error code"):
-        for _ in range(4):  # forward snapshots the word, a later call finds the snapshot non-zero
+        for _ in range(4):  # the first guard that runs after the failed launch has finished sees the code
             out = ck.linear_swiglu(x, w)
             torch.cuda.synchronize()
             out.sum().backward()
@@ -68,3 +69,26 @@ def test_operator_path_reports_an_expired_wait_without_sync():
     ck.linear_swiglu(x, w).sum().backward()
     torch.cuda.synchronize()
     ops.check_device_status(dev)
+
+
+def test_status_poll_reports_a_device_resident_word_without_sync():
+    """`coda_b200_status_poll` is the same lazy check for callers that keep the status word in device memory: snapshot,
+    event query, report once, clear."""
+    from coda_kernels_b200 import _lib
+
+    lib = _lib.lib
+    dev = torch.device(DEV)
+    word = torch.zeros(1, dtype=torch.int32, device=dev)
+    stream = torch.cuda.current_stream().cuda_stream
+    torch.cuda.synchronize()
+    assert lib.coda_b200_status_poll(word.data_ptr(), stream) == 0  # takes a snapshot of a clean word
+    torch.cuda.synchronize()
+    assert lib.coda_b200_selftest_wait_timeout(word.data_ptr(), 2000, None, stream) == 0
+    codes = []
+    for _ in range(3):  # 1st: old snapshot was clean, takes a new one; 2nd (after the kernel ended): reports; 3rd: clean again
+        torch.cuda.synchronize()
+        codes.append(lib.coda_b200_status_poll(word.data_ptr(), stream))
+    assert codes[0] == 0 and codes[1] > 0 and codes[2] == 0, codes
+    torch.cuda.synchronize()
+    assert int(word.item()) == 0, "reporting clears the device word"
+    assert lib.coda_b200_status_poll(None, None) == -1
