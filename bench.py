@@ -264,16 +264,13 @@ class Workload:
     def step(self, dev_inputs: dict | None = None, reduce_dx: bool | None = None):
         """Forward + backward through the public operator API.  Returns the result tensors.
 
-        ``reduce_dx``: all-reduce the input gradient over ranks inside the step.  ``None`` = the operator's own
-        convention: off for the column- and head-parallel operators (each rank keeps its partial sum), on for the
-        vocab-parallel cross entropy (whose wrapper overlaps the all-reduce with the weight-gradient GEMM)."""
+        ``reduce_dx``: all-reduce the input gradient over ranks inside the step (the sharded wrappers start it right
+        after the input-gradient GEMM, so that it runs under the weight-gradient GEMM).  ``None`` = off for the column-
+        and head-parallel operators (each rank keeps its partial sum), on for the vocab-parallel cross entropy."""
         ck, d = self.ck, (self.dev if dev_inputs is None else dev_inputs)
         if reduce_dx is None:
             reduce_dx = self.op == "cross_entropy"
-        res = self._step(ck, d, reduce_dx)
-        if reduce_dx and self.world > 1 and self.op != "cross_entropy":
-            self.parallel.allreduce_partial_dx(res["dx"])
-        return res
+        return self._step(ck, d, reduce_dx)
 
     def _step(self, ck, d, reduce_dx: bool):
         if self.op == "llama3_block":
@@ -286,12 +283,18 @@ class Workload:
             return {"x2": x2, "qkv": qkv, **{"d" + n: g_ for n, g_ in zip(names, grads)}}
         x = d["x"].detach().requires_grad_(True)
         w = d["weight"].detach().requires_grad_(True)
+        several = self.world > 1
         if self.op in ("swiglu", "sigmoid_glu"):
-            out = ck.linear_swiglu(x, w) if self.op == "swiglu" else ck.functional.linear_sigmoid_glu(x, w)
+            if self.op == "sigmoid_glu":
+                out = ck.functional.linear_sigmoid_glu(x, w)
+            else:
+                out = self.parallel.column_parallel_linear_swiglu(x, w, reduce_dx=reduce_dx) if several else ck.linear_swiglu(x, w)
             dx, dw = torch.autograd.grad(out, (x, w), d["dout"])
+            if self.op == "sigmoid_glu" and several and reduce_dx:
+                self.parallel.allreduce_partial_dx(dx)
             return {"out": out, "dx": dx, "dweight": dw}
         if self.op == "sigmoid":
-            out = ck.linear_sigmoid(x, w)
+            out = self.parallel.column_parallel_linear_sigmoid(x, w, reduce_dx=reduce_dx) if several else ck.linear_sigmoid(x, w)
             dx, dw = torch.autograd.grad(out, (x, w), d["dout"])
             return {"out": out, "dx": dx, "dweight": dw}
         if self.op == "cross_entropy":
@@ -304,12 +307,12 @@ class Workload:
             return {"loss": loss, "dx": dx, "dweight": dw}
         g = d["gamma"].detach().requires_grad_(True)
         hq, hk, _ = self.local_heads
-        q, k, v = ck.linear_qknorm_rope(x, w, g, d["positions"], d["frequencies"], self.shape["head_dim"], hq, hk, 1e-6)
+        if several:  # dgamma is summed over the ranks inside the wrapper
+            q, k, v = self.parallel.head_parallel_linear_qknorm_rope(x, w, g, d["positions"], d["frequencies"], self.shape["head_dim"],
+                                                                     hq, hk, 1e-6, reduce_dx=reduce_dx)
+        else:
+            q, k, v = ck.linear_qknorm_rope(x, w, g, d["positions"], d["frequencies"], self.shape["head_dim"], hq, hk, 1e-6)
         dx, dw, dg = torch.autograd.grad((q, k, v), (x, w, g), (d["dq"], d["dk"], d["dv"]))
-        if self.world > 1:
-            dg32 = dg.float()
-            torch.distributed.all_reduce(dg32)
-            dg = dg32.to(dg.dtype)
         return {"q": q, "k": k, "v": v, "dx": dx, "dweight": dw, "dgamma": dg}
 
     def download(self, results: dict) -> int:
@@ -679,7 +682,8 @@ def measure_op(b: Bench, op: str, headline: bool) -> tuple[dict, dict]:
     extra = {}
     if headline and b.world > 1 and op != "cross_entropy" and op != "llama3_block":
         with_ar = measure_device(b, wl, reduce_dx=True, with_eager=False)
-        with_ar["dx_reduction"] = "bf16 all-reduce (NCCL) of the [M, K] input gradient inside every step, after the backward GEMMs"
+        with_ar["dx_reduction"] = ("bf16 all-reduce (NCCL) of the [M, K] input gradient inside every step, issued before the "
+                                   "weight-gradient GEMM so that the two overlap")
         extra[f"{op}_with_dx_allreduce"] = with_ar
     if headline and not args.no_e2e:
         res["e2e"] = measure_e2e(b, wl)

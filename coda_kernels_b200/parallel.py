@@ -5,9 +5,14 @@ need to run column-, head- or vocab-parallel over ``torch.distributed``:
 
 * ``linear_swiglu`` / ``linear_sigmoid``: column-parallel over the output
   features (gate/up pairs stay together).  The forward needs no communication;
-  each rank's ``dx`` is a partial sum that :func:`allreduce_partial_dx` folds.
+  each rank's ``dx`` is a partial sum.  :func:`column_parallel_linear_swiglu` /
+  :func:`column_parallel_linear_sigmoid` fold it inside the backward, with the
+  all-reduce in flight while the weight-gradient GEMM runs
+  (:func:`linear_backward_overlapped`); :func:`allreduce_partial_dx` is the
+  plain fold for callers that run the unsharded operator on a weight shard.
 * ``linear_qknorm_rope``: head-parallel (whole q heads, with the k and v heads
-  of their group).  ``dgamma`` is summed over ranks, ``dx`` as above.
+  of their group), :func:`head_parallel_linear_qknorm_rope`.  ``dgamma`` is
+  summed over ranks, ``dx`` as above.
 * ``linear_cross_entropy``: vocab-parallel.  Each rank runs the fused GEMM on
   its vocabulary slice; one all-gather of per-row ``(lse, target logit)``
   (8 bytes per row per rank) gives every rank the global log-sum-exp, and the
@@ -27,8 +32,8 @@ import torch
 import torch.distributed as dist
 from torch import Tensor
 
-# CODA_B200_OVERLAP_DX=0 issues the cross-entropy input-gradient all-reduce synchronously (after it, then the weight
-# gradient GEMM) instead of letting the two overlap: a switch for measurements.
+# CODA_B200_OVERLAP_DX=0 issues the input-gradient all-reduce synchronously (after it, then the weight-gradient GEMM)
+# instead of letting the two overlap: a switch for measurements.
 OVERLAP_DX_ALLREDUCE = os.environ.get("CODA_B200_OVERLAP_DX", "1") == "1"
 
 
@@ -82,6 +87,40 @@ def allreduce_partial_dx(dx: Tensor, group: Optional[dist.ProcessGroup] = None) 
     if dist.is_initialized() and dist.get_world_size(group) > 1:
         dist.all_reduce(dx, op=dist.ReduceOp.SUM, group=group)
     return dx
+
+
+def _several_ranks(group: Optional[dist.ProcessGroup]) -> bool:
+    return dist.is_initialized() and dist.get_world_size(group) > 1
+
+
+def linear_backward_overlapped(grad_pre: Tensor, x: Tensor, weight_shard: Tensor, need_dx: bool, need_dw: bool,
+                               group: Optional[dist.ProcessGroup], reduce_dx: bool, alpha: Optional[Tensor] = None,
+                               also_reduce: Optional[Tensor] = None):
+    """``(dx, dweight)`` of ``pre = x @ weight_shard^T`` on a rank that holds a slice of the weight's rows.
+
+    ``dx = grad_pre @ weight_shard`` is this rank's partial sum.  With ``reduce_dx`` its all-reduce (bf16 on the wire)
+    is started right after the GEMM that produced it, asynchronously on the communicator's stream, and joined only
+    after the weight-gradient GEMM ``grad_pre^T @ x`` has been enqueued on this stream: the transfer over NVLink runs
+    under that GEMM.  ``also_reduce`` (e.g. a ``dgamma`` partial) is summed over the ranks the same way.
+    """
+    from . import ops
+
+    pending = []
+    several = _several_ranks(group)
+    if also_reduce is not None and several:
+        pending.append(dist.all_reduce(also_reduce, op=dist.ReduceOp.SUM, group=group, async_op=True))
+    dx = dweight = None
+    if need_dx:
+        dx = ops.gemm(grad_pre, weight_shard, alpha=alpha)
+        if reduce_dx and several:
+            pending.append(dist.all_reduce(dx, op=dist.ReduceOp.SUM, group=group, async_op=True))
+            if not OVERLAP_DX_ALLREDUCE:
+                pending.pop().wait()
+    if need_dw:
+        dweight = ops.gemm(grad_pre.mT, x, alpha=alpha)
+    for work in pending:
+        work.wait()
+    return dx, dweight
 
 
 def rebase_target(target: Tensor, vocab_start: int, vocab_local: int, ignore_index: int) -> tuple[Tensor, int]:
@@ -153,20 +192,8 @@ class VocabParallelLinearCrossEntropy(torch.autograd.Function):
         x, weight_shard, dlogits, scale = ctx.saved_tensors
         ops.lazy_status_check(x.device)
         alpha = (dloss * scale if scale is not None else dloss).reshape(1).to(dtype=torch.float32)
-        dx = dweight = pending = None
-        if ctx.needs_input_grad[0]:
-            dx = ops.gemm_scalar_scale(dlogits, weight_shard, alpha=alpha)
-            if ctx.reduce_dx and dist.is_initialized() and dist.get_world_size(ctx.group) > 1:
-                # asynchronous: the all-reduce runs on the communicator's stream while the weight-gradient GEMM
-                # below runs on this one; the streams are joined only after that GEMM has been enqueued
-                pending = dist.all_reduce(dx, op=dist.ReduceOp.SUM, group=ctx.group, async_op=True)
-                if not OVERLAP_DX_ALLREDUCE:
-                    pending.wait()
-                    pending = None
-        if ctx.needs_input_grad[1]:
-            dweight = ops.gemm_scalar_scale(dlogits.mT, x, alpha=alpha)
-        if pending is not None:
-            pending.wait()
+        dx, dweight = linear_backward_overlapped(dlogits, x, weight_shard, ctx.needs_input_grad[0], ctx.needs_input_grad[1],
+                                                 ctx.group, ctx.reduce_dx, alpha=alpha)
         return dx, dweight, None, None, None, None, None, None
 
 
@@ -184,3 +211,111 @@ def vocab_parallel_linear_cross_entropy(
     assert reduction in ("mean", "sum")
     assert target.dtype == torch.int32
     return VocabParallelLinearCrossEntropy.apply(x, weight_shard, target, vocab_start, ignore_index, reduction, group, reduce_dx)
+
+
+class ColumnParallelLinearSwiGLU(torch.autograd.Function):
+    """``linear_swiglu`` on a slice of the gate/up pairs; the output is this rank's slice of the features."""
+
+    @staticmethod
+    def forward(ctx, x, weight_shard, group, reduce_dx: bool):
+        from . import ops
+
+        ops.lazy_status_check(x.device)
+        x, weight_shard = x.contiguous(), weight_shard.contiguous()
+        preact, out = ops.swiglu_forward(x, weight_shard)
+        ctx.save_for_backward(x, weight_shard, preact)
+        ctx.group, ctx.reduce_dx = group, reduce_dx
+        return out
+
+    @staticmethod
+    def backward(ctx, grad_out):
+        from . import ops
+
+        x, weight_shard, preact = ctx.saved_tensors
+        ops.lazy_status_check(x.device)
+        grad_pre = ops.dswiglu_backward(preact, grad_out.contiguous())
+        dx, dweight = linear_backward_overlapped(grad_pre, x, weight_shard, ctx.needs_input_grad[0], ctx.needs_input_grad[1],
+                                                 ctx.group, ctx.reduce_dx)
+        return dx, dweight, None, None
+
+
+class ColumnParallelLinearSigmoid(torch.autograd.Function):
+    """``linear_sigmoid`` on a slice of the output features."""
+
+    @staticmethod
+    def forward(ctx, x, weight_shard, out_dtype, group, reduce_dx: bool):
+        from . import ops
+
+        ops.lazy_status_check(x.device)
+        x, weight_shard = x.contiguous(), weight_shard.contiguous()
+        out = ops.sigmoid_forward(x, weight_shard, out_dtype)
+        ctx.save_for_backward(x, weight_shard, out)
+        ctx.group, ctx.reduce_dx = group, reduce_dx
+        return out
+
+    @staticmethod
+    def backward(ctx, grad_out):
+        from . import ops
+
+        x, weight_shard, out = ctx.saved_tensors
+        ops.lazy_status_check(x.device)
+        grad_pre = ops.dsigmoid_backward(out, grad_out.contiguous().to(dtype=x.dtype))
+        dx, dweight = linear_backward_overlapped(grad_pre, x, weight_shard, ctx.needs_input_grad[0], ctx.needs_input_grad[1],
+                                                 ctx.group, ctx.reduce_dx)
+        return dx, dweight, None, None, None
+
+
+class HeadParallelLinearQKNormRope(torch.autograd.Function):
+    """``linear_qknorm_rope`` on this rank's q heads with the k and v heads of their groups (:func:`shard_qkv_weight`)."""
+
+    @staticmethod
+    def forward(ctx, x, weight_shard, gamma, positions, frequencies_shard, head_dim: int, num_heads_q: int, num_heads_k: int, eps: float,
+                group, reduce_dx: bool):
+        from . import ops
+
+        ops.lazy_status_check(x.device)
+        x, weight_shard = x.contiguous(), weight_shard.contiguous()
+        rotated, preact, head_mean_sq, v = ops.qknorm_rope_forward(x, weight_shard, gamma, positions, frequencies_shard, head_dim,
+                                                                   num_heads_q, num_heads_k, eps)
+        ctx.save_for_backward(x, weight_shard, gamma, positions, frequencies_shard, preact, head_mean_sq)
+        ctx.args = (head_dim, num_heads_q, num_heads_k, eps)
+        ctx.group, ctx.reduce_dx = group, reduce_dx
+        width_q = head_dim * num_heads_q
+        q, k = rotated.split((width_q, rotated.shape[1] - width_q), dim=-1)
+        return q, k, v
+
+    @staticmethod
+    def backward(ctx, grad_q, grad_k, grad_v):
+        from . import ops
+
+        x, weight_shard, gamma, positions, frequencies_shard, preact, head_mean_sq = ctx.saved_tensors
+        ops.lazy_status_check(x.device)
+        grad_v = grad_v.contiguous()
+        grad_all, dgamma = ops.qknorm_rope_bwd(grad_q.contiguous(), grad_k.contiguous(), grad_v if grad_v.shape[1] > 0 else None, preact,
+                                               head_mean_sq, gamma, positions, frequencies_shard, *ctx.args)
+        # gamma is shared by every head, so its gradient is summed over the ranks (fp32, 2 * head_dim values)
+        dx, dweight = linear_backward_overlapped(grad_all, x, weight_shard, ctx.needs_input_grad[0], ctx.needs_input_grad[1],
+                                                 ctx.group, ctx.reduce_dx, also_reduce=dgamma)
+        return (dx, dweight, dgamma.to(dtype=gamma.dtype)) + (None,) * 8
+
+
+def column_parallel_linear_swiglu(x: Tensor, weight_shard: Tensor, group: Optional[dist.ProcessGroup] = None,
+                                  reduce_dx: bool = True) -> Tensor:
+    """``linear_swiglu(x, weight)[:, this rank's features]`` for ``weight_shard = shard_swiglu_weight(weight, rank, world)``.
+    With ``reduce_dx`` the returned ``dx`` is the full input gradient on every rank."""
+    return ColumnParallelLinearSwiGLU.apply(x, weight_shard, group, reduce_dx)
+
+
+def column_parallel_linear_sigmoid(x: Tensor, weight_shard: Tensor, out_dtype: Optional[torch.dtype] = None,
+                                   group: Optional[dist.ProcessGroup] = None, reduce_dx: bool = True) -> Tensor:
+    """``linear_sigmoid(x, weight)[:, this rank's features]`` for ``weight_shard = shard_rows(weight, rank, world)``."""
+    return ColumnParallelLinearSigmoid.apply(x, weight_shard, out_dtype, group, reduce_dx)
+
+
+def head_parallel_linear_qknorm_rope(x: Tensor, weight_shard: Tensor, gamma: Tensor, positions: Tensor, frequencies_shard: Tensor,
+                                     head_dim: int, num_heads_q: int, num_heads_k: int, eps: float,
+                                     group: Optional[dist.ProcessGroup] = None, reduce_dx: bool = True):
+    """``(q, k, v)`` of this rank's heads; the head counts are the LOCAL ones, ``weight_shard`` and ``frequencies_shard`` come
+    from :func:`shard_qkv_weight`.  ``dgamma`` is summed over the ranks, and with ``reduce_dx`` so is ``dx``."""
+    return HeadParallelLinearQKNormRope.apply(x, weight_shard, gamma, positions, frequencies_shard, head_dim, num_heads_q, num_heads_k,
+                                              eps, group, reduce_dx)

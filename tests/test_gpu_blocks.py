@@ -72,7 +72,7 @@ def test_golden(golden_dir):
     for reduction in ("mean", "sum"):
         loss, grads = run_post(d, 1e-5, reduction)
         ref = g[f"post_{reduction}"]
-        assert abs(float(loss) - float(ref["loss"])) <= 2e-3 * abs(float(ref["loss"])), f"{reduction} loss {float(loss)} vs {float(ref['loss'])}"
+        assert abs(float(loss.detach()) - float(ref["loss"])) <= 2e-3 * abs(float(ref["loss"])), f"{reduction} loss {float(loss.detach())} vs {float(ref['loss'])}"
         for n in NAMES:
             close(grads[n], ref["grads"][{"w3": "w_vocab"}.get(n, n)], f"post[{reduction}] d{n}")
     torch.cuda.synchronize()
@@ -107,7 +107,7 @@ def test_gqa_layer_vs_oracle():
     loss, grads = run_post(d, eps, "mean")
     fn = functools.partial(eager.llama3_block_post, targets=dev["targets"], eps=eps)
     (rl,), g = eager.fwd_bwd(fn, {n: dev[{"w3": "w_vocab"}.get(n, n)] for n in NAMES}, NAMES, torch.tensor(1.0, device=DEV))
-    assert abs(float(loss) - float(rl)) <= 2e-3 * abs(float(rl)), f"loss {float(loss)} vs {float(rl)}"
+    assert abs(float(loss.detach()) - float(rl)) <= 2e-3 * abs(float(rl)), f"loss {float(loss.detach())} vs {float(rl)}"
     for n in NAMES:
         close(grads[n], g[n], f"post d{n}")
     torch.cuda.synchronize()

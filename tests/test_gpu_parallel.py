@@ -85,6 +85,45 @@ def _worker(rank: int, world: int, port: int, out_dir: str):
             close(a, b[:, rank * cnt * hd : (rank + 1) * cnt * hd], f"qk {n}")
         close(dx32, g["x"], "qk dx (sum of partials)")
         close(dg32, g["gamma"], "qk dgamma (sum over ranks)")
+
+        # ---- the sharded wrappers: same slices, dx all-reduced inside the backward (under the weight-gradient GEMM)
+        d = inputs.swiglu_inputs(512, 256, 512)
+        (ro,), g = eager.fwd_bwd(eager.linear_swiglu, {"x": d["x"].to(dev), "weight": d["weight"].to(dev)}, ["x", "weight"], d["dout"].to(dev))
+        lo, hi = parallel.shard_bounds(d["weight"].shape[0], rank, world, 16)
+        x, w = leaf(d["x"]), leaf(parallel.shard_swiglu_weight(d["weight"], rank, world).contiguous())
+        out = parallel.column_parallel_linear_swiglu(x, w)
+        dx, dw = torch.autograd.grad(out, (x, w), d["dout"][:, lo // 2 : hi // 2].contiguous().to(dev))
+        close(out, ro[:, lo // 2 : hi // 2], "column-parallel swiglu out")
+        close(dw, g["weight"][lo:hi], "column-parallel swiglu dweight")
+        close(dx, g["x"], "column-parallel swiglu dx (all-reduced in the backward)")
+
+        d = inputs.sigmoid_inputs(300, 256, 256)
+        (ro,), g = eager.fwd_bwd(eager.linear_sigmoid, {"x": d["x"].to(dev), "weight": d["weight"].to(dev)}, ["x", "weight"], d["dout"].to(dev))
+        lo, hi = parallel.shard_bounds(256, rank, world, 8)
+        x, w = leaf(d["x"]), leaf(parallel.shard_rows(d["weight"], rank, world).contiguous())
+        out = parallel.column_parallel_linear_sigmoid(x, w)
+        dx, dw = torch.autograd.grad(out, (x, w), d["dout"][:, lo:hi].contiguous().to(dev))
+        close(out, ro[:, lo:hi], "column-parallel sigmoid out")
+        close(dw, g["weight"][lo:hi], "column-parallel sigmoid dweight")
+        close(dx, g["x"], "column-parallel sigmoid dx (all-reduced in the backward)")
+        keep = parallel.column_parallel_linear_sigmoid(x, w, reduce_dx=False)
+        (dx_partial,) = torch.autograd.grad(keep, (x,), d["dout"][:, lo:hi].contiguous().to(dev))
+        dx32 = dx_partial.float()
+        dist.all_reduce(dx32)
+        close(dx32, g["x"], "column-parallel sigmoid dx (partials kept, summed here)")
+
+        d = inputs.qknorm_rope_inputs(200, 256, hd, hq, hk, hv, seq_len=64)
+        x, w, gm = leaf(d["x"]), leaf(lw), leaf(d["gamma"])
+        q, k, v = parallel.head_parallel_linear_qknorm_rope(x, w, gm, d["positions"].to(dev), lf.to(dev), hd, lq, lk, 1e-6)
+        dx, dw, dg = torch.autograd.grad((q, k, v), (x, w, gm), (sl(d["dq"], lq), sl(d["dk"], lk), sl(d["dv"], lv)))
+        fn = functools.partial(eager.linear_qknorm_rope, positions=d["positions"].to(dev), frequencies=d["frequencies"].to(dev),
+                               head_dim=hd, num_heads_q=hq, num_heads_k=hk, eps=1e-6)
+        outs, g = eager.fwd_bwd(fn, {n: d[n].to(dev) for n in ("x", "weight", "gamma")}, ["x", "weight", "gamma"],
+                                (d["dq"].to(dev), d["dk"].to(dev), d["dv"].to(dev)))
+        for a, b, n, cnt in ((q, outs[0], "q", lq), (k, outs[1], "k", lk), (v, outs[2], "v", lv)):
+            close(a, b[:, rank * cnt * hd : (rank + 1) * cnt * hd], f"head-parallel {n}")
+        close(dx, g["x"], "head-parallel dx (all-reduced in the backward)")
+        close(dg, g["gamma"], "head-parallel dgamma (summed over ranks in the backward)")
         torch.cuda.synchronize()
         ck.ops.check_device_status(dev)
     except Exception as ex:  # noqa: BLE001

@@ -90,6 +90,45 @@ def _lse_worker(rank: int, world: int, port: int, result_path: str):
         dist.destroy_process_group()
 
 
+def _overlap_worker(rank: int, world: int, port: int, result_path: str):
+    """The shared sharded backward on CPU ranks: the GEMMs are stood in for by torch matmuls (this test is about the
+    host-side sequencing: partial dx, asynchronous all-reduce joined after the weight gradient, dgamma summed)."""
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from coda_kernels_b200 import ops
+
+        def fake_gemm(A, B, out=None, alpha=None, out_dtype=None, C=None):
+            res = A.float() @ B.float()
+            return res * alpha if alpha is not None else res
+
+        real_gemm, ops.gemm = ops.gemm, fake_gemm
+        try:
+            g = torch.Generator().manual_seed(5)
+            x, weight, grad_pre = torch.randn(12, 8, generator=g), torch.randn(16, 8, generator=g), torch.randn(12, 16, generator=g)
+            lo, hi = parallel.shard_bounds(16, rank, world, 8)
+            dgamma = torch.full((4,), float(rank + 1))
+            alpha = torch.tensor([0.5])
+            dx, dw = parallel.linear_backward_overlapped(grad_pre[:, lo:hi], x, weight[lo:hi], True, True, None, True, alpha=alpha,
+                                                         also_reduce=dgamma)
+            dx_keep, _ = parallel.linear_backward_overlapped(grad_pre[:, lo:hi], x, weight[lo:hi], True, False, None, False)
+            ok = (torch.allclose(dx, 0.5 * grad_pre @ weight, atol=1e-5) and torch.allclose(dw, 0.5 * grad_pre[:, lo:hi].T @ x, atol=1e-5)
+                  and torch.equal(dgamma, torch.full((4,), 3.0)) and torch.allclose(dx_keep, grad_pre[:, lo:hi] @ weight[lo:hi], atol=1e-5))
+        finally:
+            ops.gemm = real_gemm
+        if rank == 0:
+            with open(result_path, "w") as f:
+                f.write(str(int(ok)))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_sharded_backward_reduces_dx_and_dgamma_two_ranks(tmp_path):
+    out = tmp_path / "result.txt"
+    mp.spawn(_overlap_worker, args=(2, _free_port(), str(out)), nprocs=2, join=True)
+    assert out.read_text() == "1"
+
+
 def test_vocab_parallel_lse_exchange_two_ranks(tmp_path):
     out = tmp_path / "result.txt"
     mp.spawn(_lse_worker, args=(2, _free_port(), str(out)), nprocs=2, join=True)
