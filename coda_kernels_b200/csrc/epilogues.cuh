@@ -195,8 +195,10 @@ enum class Act { kNone, kSigmoid };
 template <typename OutT, Act kAct>
 struct EpiStore {
   static constexpr uint32_t kLoadRingBytes = 0;
+  static constexpr bool kSplitTail = true;  // can park a partial accumulator in the tail-split workspace
   struct Params {
-    alignas(64) CUtensorMap tm_d;  // D as [M, N], box 32 x 32
+    alignas(64) CUtensorMap tm_d;   // D as [M, N], box 32 x 32
+    alignas(64) CUtensorMap tm_ws;  // tail-split workspace as [slabs * tile rows, kBN] fp32, box 32 x 32 (unused otherwise)
     OutT* D;
     long long ldd;
     const float* alpha;  // device scalar or nullptr (= 1)
@@ -204,10 +206,25 @@ struct EpiStore {
     long long ldc;
     int c_is_fp32;
     int use_tma;
+    float* ws = nullptr;     // host side: tail-split workspace offered by the caller (nullptr: whole tiles only)
+    long long ws_bytes = 0;
   };
 
   template <int kBN>
   __device__ static void run(const Params& p, EpiCtx& c) {
+    if (c.part_row0 >= 0) {
+      // One part of a tail tile: the raw fp32 accumulator goes to its workspace slab (always through the staging
+      // ring and TMA stores; the slab is a whole tile, so nothing is clipped).  alpha, the conversion and the store
+      // to D happen when the parts are added.
+      for_chunks(c.taddr, kBN / 32, [&](int ch, float* v) {
+        const uint32_t tile = ring_acquire(c);
+        stage_row_f32(tile, c.lane, v);
+        ring_publish();
+        if (c.lane == 0) tma_store_2d(&p.tm_ws, tile, ch * 32, c.part_row0);
+        ring_commit(c);
+      });
+      return;
+    }
     const float alpha = p.alpha ? __ldg(p.alpha) : 1.0f;
     const bool row_ok = c.row < c.M;
     OutT* drow = p.D + static_cast<long long>(c.row) * p.ldd + c.n0;

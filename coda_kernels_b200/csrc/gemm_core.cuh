@@ -34,6 +34,10 @@ struct GemmShape {
   int tiles_m;  // number of (kBlockM * kCtaGroup)-row tiles
   int tiles_n;  // number of kBN-column tiles
   int group_m;  // raster: tiles of `group_m` consecutive row-tiles share their column sweep (L2 reuse)
+  // Tail split (sk_split <= 1: off).  Tiles go to the clusters round-robin, so the last `sk_tail` tiles (fewer than
+  // there are clusters) would keep only `sk_tail` clusters busy for a whole contraction.  With sk_split = s each of them is
+  // cut into s equal ranges of k-blocks that run as separate items, accumulated in parts (see WorkItem).
+  int sk_tail, sk_split;
   // Measurement aid (0 = off): while the mainloop of a tile runs, each epilogue warp issues this many bytes of
   // coalesced global loads from [probe_src, probe_src + probe_span) and of shared-memory stores per k-block, i.e. the
   // load/store-unit traffic an operand-transforming prologue would add, without changing any result.
@@ -52,6 +56,8 @@ struct EpiCtx {
   int tn;          // column-tile index
   int M, N;        // problem extents
   uint32_t taddr;  // TMEM address of (this warp's first lane, first column of the accumulator)
+  int part_row0;   // -1: the accumulator is the whole contraction; else a partial sum, and this is the workspace row that
+                   // lane 0's row goes to (tail split; only epilogues with kSplitTail are ever launched that way)
   int lane;
   uint32_t ring;   // shared-memory address of this warp's staging ring (kRingSlots slots of kRingSlotBytes)
   uint32_t slot;   // slot the next staged sub-tile goes to
@@ -99,6 +105,49 @@ __device__ __forceinline__ void tile_coords(const GemmShape& s, int tile, int& t
   tm = first_m + r % gsz;
   tn = r / gsz;
 }
+
+// One pass of a role's loop: k-blocks [kb0, kb1) of `tile`.  slab < 0: the whole contraction, the epilogue writes the
+// output.  Otherwise the item is one part of a tail tile, and its accumulator goes, as raw fp32, to slab `slab` of the
+// workspace; a follow-up kernel adds a tile's parts in a fixed order (so results do not depend on timing), applies
+// alpha and writes the output.
+struct WorkItem {
+  int tile, kb0, kb1, slab;
+};
+
+// Every role of a CTA walks the same item sequence, computed from the launch geometry alone: items
+// cluster_id, cluster_id + num_clusters, ... of [whole tiles 0 .. F-1 | parts of the tail tiles], F = num_tiles - sk_tail.
+// Tail items are ordered part-major (part 0 of every tail tile, then part 1, ...): the clusters that run concurrently
+// then work on neighbouring tiles at the same depth of the contraction, which is what lets them share operand tiles
+// through L2.
+struct WorkSchedule {
+  int num_kb, num_clusters, full, tail, split, total, next_item;
+
+  __device__ WorkSchedule(const GemmShape& s, int cluster, int clusters, int tiles, int kbs)
+      : num_kb(kbs), num_clusters(clusters), next_item(cluster) {
+    split = s.sk_split > 1 ? s.sk_split : 1;
+    tail = split > 1 ? s.sk_tail : 0;
+    full = tiles - tail;
+    total = full + tail * split;
+  }
+  __device__ bool next(WorkItem& w) {
+    if (next_item >= total) return false;
+    const int i = next_item;
+    next_item += num_clusters;
+    if (i < full) {
+      w.tile = i;
+      w.kb0 = 0;
+      w.kb1 = num_kb;
+      w.slab = -1;
+    } else {
+      const int j = i - full, part = j / tail;
+      w.tile = full + (j - part * tail);
+      w.kb0 = static_cast<int>(static_cast<long long>(part) * num_kb / split);
+      w.kb1 = static_cast<int>(static_cast<long long>(part + 1) * num_kb / split);
+      w.slab = j;
+    }
+    return true;
+  }
+};
 
 // What-if traffic for the prologue-fusion study (see GemmShape): runs in an epilogue warp while it would otherwise
 // spin on the accumulator barrier, stops as soon as the accumulator is complete.
@@ -245,12 +294,14 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
       const uint32_t full_sig = (kCtaGroup == 2) ? mapa(bar_full, 0) : bar_full;  // the leader's barriers
       uint32_t s = 0, ph = 0;
       bool ok = true;
-      for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters) {
+      WorkSchedule sched(shape, cluster_id, num_clusters, num_tiles, num_kb);
+      WorkItem w;
+      while (ok && sched.next(w)) {
         int tm, tn;
-        tile_coords(shape, tile, tm, tn);
+        tile_coords(shape, w.tile, tm, tn);
         const int a_row0 = tm * (kBlockM * kCtaGroup) + static_cast<int>(rank) * kBlockM;
         const int b_row0 = tn * kBN + static_cast<int>(rank) * kBNcta;
-        for (int kb = 0; kb < num_kb; ++kb) {
+        for (int kb = w.kb0; kb < w.kb1; ++kb) {
           if (!mbar_wait(bar_empty + 8 * s, ph ^ 1u, abort_word, kErrTimeoutEmpty)) {
             ok = false;
             break;
@@ -316,7 +367,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
       const uint32_t b_lbo = kBMn ? lbo_mn : 16u, b_sbo = kBMn ? sbo_mn : 1024u, b_step = kBMn ? 2048u : 32u;
       uint32_t s = 0, ph = 0, it = 0;
       bool ok = true;
-      for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters, ++it) {
+      WorkSchedule sched(shape, cluster_id, num_clusters, num_tiles, num_kb);
+      WorkItem w;
+      for (; ok && sched.next(w); ++it) {
         const uint32_t acc = it & 1u, aph = (it >> 1) & 1u;
         if (!mbar_wait(bar_acc_empty + 8 * acc, aph ^ 1u, abort_word, kErrTimeoutAccEmpty)) {
           ok = false;
@@ -324,7 +377,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
         }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * kBN;
-        for (int kb = 0; kb < num_kb; ++kb) {
+        for (int kb = w.kb0; kb < w.kb1; ++kb) {
           if (!mbar_wait(bar_full + 8 * s, ph, abort_word, kErrTimeoutFull)) {
             ok = false;
             break;
@@ -336,7 +389,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
           for (int k = 0; k < kBlockK / kUmmaK; ++k) {
             const uint64_t adesc = make_smem_desc(a_addr + k * a_step, a_lbo, a_sbo);
             const uint64_t bdesc = make_smem_desc(b_addr + k * b_step, b_lbo, b_sbo);
-            umma_bf16<kCtaGroup>(d_tmem, adesc, bdesc, idesc, (kb | k) != 0 ? 1u : 0u);
+            umma_bf16<kCtaGroup>(d_tmem, adesc, bdesc, idesc, (kb != w.kb0 || k != 0) ? 1u : 0u);
           }
           umma_commit<kCtaGroup>(bar_empty + 8 * s);  // frees the stage (in both CTAs) once these MMAs retire
           if (++s == kStages) {
@@ -365,11 +418,13 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
       const int Kc = shape.K;
       uint32_t s = 0, ph = 0;
       bool ok = true;
-      for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters) {
+      WorkSchedule sched(shape, cluster_id, num_clusters, num_tiles, num_kb);
+      WorkItem w;
+      while (ok && sched.next(w)) {
         int tm, tn;
-        tile_coords(shape, tile, tm, tn);
+        tile_coords(shape, w.tile, tm, tn);
         const int a_row0 = tm * (kBlockM * kCtaGroup) + static_cast<int>(rank) * kBlockM;
-        for (int kb = 0; kb < num_kb; ++kb) {
+        for (int kb = w.kb0; kb < w.kb1; ++kb) {
           if (!mbar_wait(ctrl + kRawBarOffset + 8 * s, ph, abort_word, kErrTimeoutFull)) {
             ok = false;
             break;
@@ -416,11 +471,13 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
     c.ld_phase = 0;
     c.abort_word = abort_word;
     uint32_t it = 0;
-    for (int tile = cluster_id; tile < num_tiles; tile += num_clusters, ++it) {
+    WorkSchedule sched(shape, cluster_id, num_clusters, num_tiles, num_kb);
+    WorkItem w;
+    for (; sched.next(w); ++it) {
       int tm, tn;
-      tile_coords(shape, tile, tm, tn);
+      tile_coords(shape, w.tile, tm, tn);
       const uint32_t acc = it & 1u, aph = (it >> 1) & 1u;
-      if (shape.probe_ld_bytes + shape.probe_st_bytes != 0) probe_lsu_traffic(shape, c, bar_acc_full + 8 * acc, aph, num_kb, warp - 2);
+      if (shape.probe_ld_bytes + shape.probe_st_bytes != 0) probe_lsu_traffic(shape, c, bar_acc_full + 8 * acc, aph, w.kb1 - w.kb0, warp - 2);
       bool ok = mbar_wait(bar_acc_full + 8 * acc, aph, abort_word, kErrTimeoutAccFull);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) {
@@ -434,6 +491,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
       c.n0 = tn * kBN;
       c.tn = tn;
       c.taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * kBN;
+      c.part_row0 = w.slab < 0 ? -1 : w.slab * (kBlockM * kCtaGroup) + static_cast<int>(rank) * kBlockM + q * 32;
       Epi::template run<kBN>(ep, c);
       tc_fence_before();
       __syncwarp();

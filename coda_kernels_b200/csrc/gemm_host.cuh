@@ -3,11 +3,13 @@
 // here allocates device memory or synchronises the device.
 #pragma once
 
+#include <algorithm>
 #include <atomic>
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
 #include <string>
+#include <type_traits>
 
 #include "epilogues.cuh"
 
@@ -36,6 +38,7 @@ struct Options {
   std::atomic<int> max_ctas{0};   // cap on the persistent grid; 0 = all SMs
   std::atomic<int> tile_n{0};     // 0 = choose per problem; 64, 128 or 256 forces the column-tile width where it is built
   std::atomic<int> epi_tma{1};    // 1 = epilogues stage their output in shared memory and store it with TMA; 0 = per-thread stores
+  std::atomic<int> split_tail{1};  // 1 = a plain GEMM given a workspace may cut the tiles of its last round along K
   // Measurement aid: KB of extra global loads / shared stores per k-block and CTA issued by the epilogue warps while the
   // mainloop runs (the traffic an operand-transforming prologue would add); results are unaffected.  0 = off.
   std::atomic<int> probe_ld_kb{0};
@@ -145,12 +148,90 @@ inline int sm_count() {
 
 // The options one launch works with, read once.
 struct LaunchOptions {
-  int cta_group, group_m, max_ctas, tile_n, epi_tma, probe_ld_kb, probe_st_kb;
+  int cta_group, group_m, max_ctas, tile_n, epi_tma, probe_ld_kb, probe_st_kb, split_tail;
 };
 inline LaunchOptions launch_options() {
   const Options& o = options();
   return LaunchOptions{o.cta_group.load(), o.group_m.load(), o.max_ctas.load(), o.tile_n.load(),
-                       o.epi_tma.load(),   o.probe_ld_kb.load(), o.probe_st_kb.load()};
+                       o.epi_tma.load(),   o.probe_ld_kb.load(), o.probe_st_kb.load(), o.split_tail.load()};
+}
+
+// ------------------------------------------------------------------ tail split
+// Does the epilogue type know how to park a partial accumulator in the workspace?
+template <class E, class = void>
+struct has_split_tail : std::false_type {};
+template <class E>
+struct has_split_tail<E, std::enable_if_t<E::kSplitTail>> : std::true_type {};
+
+// Tiles are dealt to the CTA pairs round-robin; the `tail = num_tiles mod clusters` tiles of the last round keep only
+// `tail` clusters busy for a whole contraction.  Cutting each tail tile into `split` ranges of k-blocks shortens that
+// round to ceil(tail * split / clusters) * num_kb / split k-blocks, at the price of one fp32 round trip of every tail
+// tile through the workspace and a follow-up kernel.  Returns the split (1 = leave the schedule alone): the one that
+// minimises the tail's length in k-blocks, if it saves at least 15 % of it.  The workspace holds at most
+// 2 * clusters partial tiles.
+constexpr int kSplitOverheadKb = 12;  // partial epilogue + the follow-up pass, in k-block times
+inline int plan_tail_split(long long num_tiles, int num_kb, int clusters, int* tail_out) {
+  const int tail = static_cast<int>(num_tiles % clusters);
+  *tail_out = tail;
+  if (tail == 0 || clusters < 2 || num_kb < 16) return 1;
+  const int max_split = std::min(std::min(2 * clusters / tail, num_kb / 8), 64);
+  int best = 1;
+  long long best_cost = num_kb;
+  for (int s = 2; s <= max_split; ++s) {
+    const long long rounds = (static_cast<long long>(tail) * s + clusters - 1) / clusters;
+    const long long cost = rounds * ((num_kb + s - 1) / s) + kSplitOverheadKb;
+    if (cost < best_cost) {
+      best_cost = cost;
+      best = s;
+    }
+  }
+  return (best > 1 && best_cost * 100 <= static_cast<long long>(num_kb) * 85) ? best : 1;
+}
+inline long long split_workspace_bytes(int clusters, int tile_m, int bn) {
+  return 2LL * clusters * tile_m * bn * static_cast<long long>(sizeof(float));
+}
+inline int full_clusters(const LaunchOptions& opt, int cta_group) {
+  int sms = sm_count();
+  if (opt.max_ctas > 0 && opt.max_ctas < sms) sms = opt.max_ctas;
+  const int clusters = sms / cta_group;
+  return clusters < 1 ? 1 : clusters;
+}
+
+// Adds the parts of every tail tile (in part order: the result does not depend on timing), applies alpha, converts
+// and writes the tile to D.  Block (t, b) handles rows 16 b .. 16 b + 15 of tail tile t, one 16-byte group of four columns
+// per thread and pass.
+constexpr int kFinalizeRows = 16;
+template <typename OutT>
+__global__ void __launch_bounds__(256) split_finalize_kernel(const float* __restrict__ ws, OutT* __restrict__ D, long long ldd,
+                                                             GemmShape shape, int first_tail_tile, int tile_m, int bn,
+                                                             const float* __restrict__ alpha) {
+  int tm, tn;
+  tile_coords(shape, first_tail_tile + static_cast<int>(blockIdx.x), tm, tn);
+  const float a = alpha != nullptr ? __ldg(alpha) : 1.0f;
+  const int groups = bn / 4;
+  const long long slab_stride = static_cast<long long>(tile_m) * bn;  // floats per slab
+#pragma unroll 4
+  for (int idx = threadIdx.x; idx < kFinalizeRows * groups; idx += 256) {
+    const int r = blockIdx.y * kFinalizeRows + idx / groups, g = idx % groups;
+    const int row = tm * tile_m + r, col = tn * bn + g * 4;
+    if (row >= shape.M || col >= shape.N) continue;  // N is a multiple of 8: a group of 4 is all in or all out
+    // part p of tail tile t sits in slab p * sk_tail + t
+    const float* src = ws + blockIdx.x * slab_stride + static_cast<long long>(r) * bn + g * 4;
+    float4 acc = __ldcs(reinterpret_cast<const float4*>(src));
+    for (int part = 1; part < shape.sk_split; ++part) {
+      const float4 v = __ldcs(reinterpret_cast<const float4*>(src + static_cast<long long>(part) * shape.sk_tail * slab_stride));
+      acc.x += v.x;
+      acc.y += v.y;
+      acc.z += v.z;
+      acc.w += v.w;
+    }
+    OutT* dst = D + static_cast<long long>(row) * ldd + col;
+    if constexpr (sizeof(OutT) == 4) {
+      *reinterpret_cast<float4*>(dst) = make_float4(acc.x * a, acc.y * a, acc.z * a, acc.w * a);
+    } else {
+      *reinterpret_cast<uint2*>(dst) = make_uint2(pack_bf16x2(acc.x * a, acc.y * a), pack_bf16x2(acc.z * a, acc.w * a));
+    }
+  }
 }
 
 // With a prologue policy (`Pro`, see gemm_core.cuh) `a_ptr` is the raw matrix that TMA loads into the A slot and the
@@ -186,6 +267,20 @@ int launch_gemm_cfg(const void* a_ptr, long long lda, const void* b_ptr, long lo
   if ((kAMn ? lda != M : lda != K)) shape.probe_ld_bytes = 0;  // strided operand: no dense span to read from
   const long long num_tiles = static_cast<long long>(shape.tiles_m) * shape.tiles_n;
   if (num_tiles <= 0 || num_tiles > 0x7fffffffLL) return fail(kBadArgument, "tile count out of range");
+  const int num_kb = (K + kBlockK - 1) / kBlockK;
+  shape.sk_tail = 0;
+  shape.sk_split = 1;
+  typename Epi::Params ep_sk = ep;  // what the kernel receives (gains the workspace map if the tail is split)
+  if constexpr (has_split_tail<Epi>::value && std::is_same<Pro, ProNone>::value) {
+    const int all = full_clusters(opt, kCtaGroup);
+    if (opt.split_tail != 0 && ep.ws != nullptr && ep.ws_bytes >= split_workspace_bytes(all, tile_m, kBN)) {
+      shape.sk_split = plan_tail_split(num_tiles, num_kb, all, &shape.sk_tail);
+      if (shape.sk_split > 1) {
+        rc = make_tmap_out(&ep_sk.tm_ws, ep.ws, kBN, 2LL * all * tile_m, kBN);
+        if (rc != kOk) return rc;
+      }
+    }
+  }
 
   auto kern = gemm_kernel<kCtaGroup, kBN, kAMn, kBMn, Epi, Pro>;
   // One bit per device: setting the attribute twice is harmless, so two threads racing here only repeat the call.
@@ -205,7 +300,7 @@ int launch_gemm_cfg(const void* a_ptr, long long lda, const void* b_ptr, long lo
   if (opt.max_ctas > 0 && opt.max_ctas < sms) sms = opt.max_ctas;
   int clusters = sms / kCtaGroup;
   if (clusters < 1) clusters = 1;
-  if (clusters > num_tiles) clusters = static_cast<int>(num_tiles);
+  if (clusters > num_tiles && shape.sk_split <= 1) clusters = static_cast<int>(num_tiles);
 
   cudaLaunchConfig_t cfg;
   memset(&cfg, 0, sizeof(cfg));
@@ -222,8 +317,17 @@ int launch_gemm_cfg(const void* a_ptr, long long lda, const void* b_ptr, long lo
     cfg.attrs = attr;
     cfg.numAttrs = 1;
   }
-  cudaError_t e = cudaLaunchKernelEx(&cfg, kern, ta, tb, shape, ep, status, pp);
+  cudaError_t e = cudaLaunchKernelEx(&cfg, kern, ta, tb, shape, ep_sk, status, pp);
   if (e != cudaSuccess) return fail(kCudaError, std::string("GEMM launch failed: ") + cudaGetErrorString(e));
+  if constexpr (has_split_tail<Epi>::value && std::is_same<Pro, ProNone>::value) {
+    if (shape.sk_split > 1) {
+      const dim3 grid(static_cast<unsigned>(shape.sk_tail), static_cast<unsigned>(tile_m / kFinalizeRows), 1);
+      split_finalize_kernel<<<grid, 256, 0, stream>>>(ep.ws, ep.D, ep.ldd, shape, static_cast<int>(num_tiles) - shape.sk_tail, tile_m, kBN,
+                                                       ep.alpha);
+      e = cudaGetLastError();
+      if (e != cudaSuccess) return fail(kCudaError, std::string("tail-split follow-up launch failed: ") + cudaGetErrorString(e));
+    }
+  }
   return kOk;
 }
 
@@ -266,6 +370,16 @@ int launch_gemm(const Operand& A, const Operand& B, int M, int N, int K, typenam
   const bool two = opt.cta_group == 2;
   int tile_n = 256;
   if constexpr (kNarrow > 0) tile_n = choose_tile_n(M, N, opt, kNarrow == 2 && !a_mn && !b_mn);
+  if constexpr (has_split_tail<Epi>::value) {
+    // with a workspace, a wide output whose tiles do not fill the last round is balanced by splitting that round's
+    // tiles instead of by narrower tiles
+    const int group = two ? 2 : 1;
+    const long long tiles256 = static_cast<long long>((M + kBlockM * group - 1) / (kBlockM * group)) * ((N + 255) / 256);
+    int tail = 0;
+    if (opt.split_tail != 0 && ep.ws != nullptr && N > 128 &&
+        plan_tail_split(tiles256, (K + kBlockK - 1) / kBlockK, full_clusters(opt, group), &tail) > 1)
+      tile_n = 256;
+  }
 #define CB_LAUNCH_BN(BN, AM, BM)                                                                                   \
   (two ? launch_gemm_cfg<2, BN, AM, BM, Epi>(A.ptr, lda, B.ptr, ldb, M, N, K, ep, status, stream, opt)               \
        : launch_gemm_cfg<1, BN, AM, BM, Epi>(A.ptr, lda, B.ptr, ldb, M, N, K, ep, status, stream, opt))

@@ -27,6 +27,9 @@ extern "C" int coda_b200_set_option(const char* name, int value) {
   } else if (!strcmp(name, "epi_tma")) {
     if (value != 0 && value != 1) return fail(kBadArgument, "epi_tma must be 0 or 1");
     o.epi_tma = value;
+  } else if (!strcmp(name, "split_tail")) {
+    if (value != 0 && value != 1) return fail(kBadArgument, "split_tail must be 0 or 1");
+    o.split_tail = value;
   } else if (!strcmp(name, "probe_ld_kb") || !strcmp(name, "probe_st_kb")) {
     if (value < 0 || value > 256) return fail(kBadArgument, "probe traffic must be between 0 and 256 KB per k-block");
     (name[6] == 'l' ? o.probe_ld_kb : o.probe_st_kb) = value;
@@ -39,7 +42,8 @@ extern "C" int coda_b200_set_option(const char* name, int value) {
 namespace {
 template <typename OutT, Act kAct>
 int run_store(const void* A, int64_t asm_, int64_t ask, const void* B, int64_t bsk, int64_t bsn, const void* C, int64_t ldc,
-              int c_is_fp32, void* D, int64_t ldd, int M, int N, int K, const float* alpha, int* dev_status, void* stream) {
+              int c_is_fp32, void* D, int64_t ldd, int M, int N, int K, const float* alpha, int* dev_status, void* stream,
+              void* workspace = nullptr, int64_t workspace_bytes = 0) {
   if (D == nullptr || A == nullptr || B == nullptr) return fail(kBadArgument, "NULL matrix pointer");
   if ((reinterpret_cast<uintptr_t>(D) & 15u) != 0) return fail(kBadArgument, "D must be 16-byte aligned");
   if (N % 8 != 0 || ldd % 8 != 0 || ldd < N) return fail(kBadArgument, "N and ldd must be multiples of 8 with ldd >= N");
@@ -52,6 +56,11 @@ int run_store(const void* A, int64_t asm_, int64_t ask, const void* B, int64_t b
   ep.C = C;
   ep.ldc = ldc;
   ep.c_is_fp32 = c_is_fp32;
+  if (kAct == Act::kNone && C == nullptr && workspace != nullptr) {  // a plain GEMM may be split along K
+    if ((reinterpret_cast<uintptr_t>(workspace) & 15u) != 0) return fail(kBadArgument, "workspace must be 16-byte aligned");
+    ep.ws = static_cast<float*>(workspace);
+    ep.ws_bytes = workspace_bytes;
+  }
   int rc = make_tmap_out(&ep.tm_d, ep.D, N, M, ldd);
   if (rc != kOk) return rc;
   Operand a{A, asm_, ask};
@@ -68,6 +77,29 @@ extern "C" int coda_b200_gemm_add(const void* A, int64_t a_stride_m, int64_t a_s
                                         alpha, dev_status, stream);
   return run_store<__nv_bfloat16, Act::kNone>(A, a_stride_m, a_stride_k, B, b_stride_k, b_stride_n, C, ldc, c_is_fp32, D, ldd, M, N,
                                               K, alpha, dev_status, stream);
+}
+
+extern "C" int64_t coda_b200_gemm_workspace_bytes(int M, int N, int K) {
+  if (M <= 0 || N <= 128 || K <= 0) return 0;  // narrow outputs keep their narrow tiles
+  const LaunchOptions opt = launch_options();
+  if (opt.split_tail == 0) return 0;
+  const int group = opt.cta_group == 2 ? 2 : 1;
+  const int tile_m = kBlockM * group, clusters = full_clusters(opt, group);
+  const long long tiles = static_cast<long long>((M + tile_m - 1) / tile_m) * ((N + 255) / 256);
+  int tail = 0;
+  if (plan_tail_split(tiles, (K + kBlockK - 1) / kBlockK, clusters, &tail) <= 1) return 0;
+  return split_workspace_bytes(clusters, tile_m, 256);
+}
+
+extern "C" int coda_b200_gemm_ws(const void* A, int64_t a_stride_m, int64_t a_stride_k, const void* B, int64_t b_stride_k,
+                                 int64_t b_stride_n, void* D, int64_t ldd, int d_is_fp32, int M, int N, int K, const float* alpha,
+                                 void* workspace, int64_t workspace_bytes, int* dev_status, void* stream) {
+  if (workspace_bytes < 0) return fail(kBadArgument, "workspace_bytes must not be negative");
+  if (d_is_fp32)
+    return run_store<float, Act::kNone>(A, a_stride_m, a_stride_k, B, b_stride_k, b_stride_n, nullptr, 0, 0, D, ldd, M, N, K, alpha,
+                                        dev_status, stream, workspace, workspace_bytes);
+  return run_store<__nv_bfloat16, Act::kNone>(A, a_stride_m, a_stride_k, B, b_stride_k, b_stride_n, nullptr, 0, 0, D, ldd, M, N, K,
+                                              alpha, dev_status, stream, workspace, workspace_bytes);
 }
 
 extern "C" int coda_b200_gemm(const void* A, int64_t a_stride_m, int64_t a_stride_k, const void* B, int64_t b_stride_k,

@@ -29,11 +29,23 @@ inline const void* ptr_or_null(const OptTensor& t) { return t.has_value() ? t->d
 
 void gemm_out(const Tensor& A, const Tensor& B, Tensor& out, const OptTensor& alpha, const OptTensor& C, const Tensor& status) {
   const c10::cuda::CUDAGuard guard(A.device());
-  check(coda_b200_gemm_add(A.data_ptr(), A.stride(0), A.stride(1), B.data_ptr(), B.stride(0), B.stride(1), ptr_or_null(C),
-                           C.has_value() ? C->stride(0) : 0, C.has_value() && C->scalar_type() == at::kFloat, out.data_ptr(),
-                           out.stride(0), out.scalar_type() == at::kFloat, static_cast<int>(A.size(0)), static_cast<int>(B.size(1)),
-                           static_cast<int>(A.size(1)), alpha.has_value() ? alpha->data_ptr<float>() : nullptr, status_ptr(status),
-                           stream_of(A)),
+  const int M = static_cast<int>(A.size(0)), N = static_cast<int>(B.size(1)), K = static_cast<int>(A.size(1));
+  const float* alpha_ptr = alpha.has_value() ? alpha->data_ptr<float>() : nullptr;
+  if (!C.has_value()) {
+    // A plain product may be balanced by stream-K; its fp32 workspace (the one allocation of this layer's `*_out` ops)
+    // comes from the caching allocator and is only asked for when the library would use it.
+    const int64_t ws_bytes = coda_b200_gemm_workspace_bytes(M, N, K);
+    Tensor ws;
+    if (ws_bytes > 0) ws = at::empty({ws_bytes / 4}, A.options().dtype(at::kFloat));
+    check(coda_b200_gemm_ws(A.data_ptr(), A.stride(0), A.stride(1), B.data_ptr(), B.stride(0), B.stride(1), out.data_ptr(), out.stride(0),
+                            out.scalar_type() == at::kFloat, M, N, K, alpha_ptr, ws_bytes > 0 ? ws.data_ptr() : nullptr, ws_bytes,
+                            status_ptr(status), stream_of(A)),
+          "gemm");
+    return;
+  }
+  check(coda_b200_gemm_add(A.data_ptr(), A.stride(0), A.stride(1), B.data_ptr(), B.stride(0), B.stride(1), C->data_ptr(), C->stride(0),
+                           C->scalar_type() == at::kFloat, out.data_ptr(), out.stride(0), out.scalar_type() == at::kFloat, M, N, K,
+                           alpha_ptr, status_ptr(status), stream_of(A)),
         "gemm");
 }
 

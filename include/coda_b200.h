@@ -48,7 +48,9 @@ const char* coda_b200_last_error(void);
 /* Tuning switches: "cta_group" (1 or 2), "group_m", "max_ctas", "tile_n"
  * (0 = automatic, 64, 128, 256; plain and sigmoid GEMMs only), "epi_tma"
  * (1 = epilogues stage output tiles in shared memory and write them with TMA
- * stores, the default; 0 = per-thread 16-byte stores).  Options are
+ * stores, the default; 0 = per-thread 16-byte stores), "split_tail" (1 = a plain
+ * GEMM that is given a workspace may cut the tiles of its last round along K, the
+ * default; 0 = never: see coda_b200_gemm_ws).  Options are
  * process-wide atomics: a launch reads them once at its start, so changing one
  * from another host thread is safe and affects later launches only.
  * "probe_ld_kb" / "probe_st_kb" (0 = off) are a measurement aid: KB of extra
@@ -90,6 +92,21 @@ int coda_b200_gemm(const void* A, int64_t a_stride_m, int64_t a_stride_k, const 
 int coda_b200_gemm_add(const void* A, int64_t a_stride_m, int64_t a_stride_k, const void* B, int64_t b_stride_k,
                        int64_t b_stride_n, const void* C, int64_t ldc, int c_is_fp32, void* D, int64_t ldd, int d_is_fp32,
                        int M, int N, int K, const float* alpha, int* dev_status, void* stream);
+
+/* The same product as coda_b200_gemm with a caller-provided workspace that lets the library shorten the last round of
+ * its persistent grid.  Tiles are dealt to the CTA pairs round-robin, so the `tiles mod pairs` tiles of the last
+ * round keep that many pairs busy for a whole contraction while the rest idle.  With a workspace each of those tiles
+ * is cut into equal ranges of k-blocks that run as separate work items; their fp32 partial accumulators go to
+ * `workspace` and a follow-up kernel adds them in a fixed order, scales, converts and writes the tile (reproducible run
+ * to run; the last bit may differ from the uncut product).  coda_b200_gemm_workspace_bytes(M, N, K) says how much
+ * workspace such a launch wants under the current options: 0 when the schedule would be left alone (the cut must save
+ * at least 15 % of the last round; option "split_tail" = 0 switches it off), in which case workspace may be NULL and
+ * the call equals coda_b200_gemm.  A smaller workspace than asked for is not an error: the launch then runs whole tiles.
+ * No counterpart in the reference (quack's persistent tile scheduler, coda/core/gemm/gemm_interface.py:103-143). */
+int64_t coda_b200_gemm_workspace_bytes(int M, int N, int K);
+int coda_b200_gemm_ws(const void* A, int64_t a_stride_m, int64_t a_stride_k, const void* B, int64_t b_stride_k,
+                      int64_t b_stride_n, void* D, int64_t ldd, int d_is_fp32, int M, int N, int K, const float* alpha,
+                      void* workspace, int64_t workspace_bytes, int* dev_status, void* stream);
 
 /* Input gradient of linear_sigmoid with the activation gradient fused into the
  * GEMM's A-operand path: dx[M, K] = G[M, N] @ W[N, K] where G = dout * out *

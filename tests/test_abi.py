@@ -82,7 +82,7 @@ def test_options_accept_only_documented_values():
     from coda_kernels_b200 import _lib
 
     lib = _lib.lib
-    for name, bad, good in ((b"tile_n", 96, 0), (b"epi_tma", 2, 1), (b"group_m", -1, 0), (b"max_ctas", -5, 0),
+    for name, bad, good in ((b"tile_n", 96, 0), (b"epi_tma", 2, 1), (b"split_tail", 2, 1), (b"group_m", -1, 0), (b"max_ctas", -5, 0),
                             (b"probe_ld_kb", 1000, 0), (b"probe_st_kb", -1, 0)):
         assert lib.coda_b200_set_option(name, bad) == -1
         assert lib.coda_b200_set_option(name, good) == 0

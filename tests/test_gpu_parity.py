@@ -301,6 +301,38 @@ def test_gemm_operand_layouts(ck, a_t, b_t):
     close(out32, 0.25 * ref, tol=1e-5, what="fp32 out with alpha")
 
 
+@pytest.mark.parametrize("M,N,K,a_t,b_t", [
+    (512, 1024, 8192, False, False),   # 8 tiles, long contraction: every tile is accumulated in nine parts
+    (768, 1024, 4096, True, True),     # weight-gradient layout (both operands MN-major), 12 tiles
+    (300, 520, 8200, False, True),     # input-gradient layout; ragged in M, N and K
+    (9728, 512, 2048, False, False),   # 76 tiles: one full round of whole tiles, then two tiles cut in four
+])
+def test_gemm_tail_split_matches_the_whole_tile_schedule(ck, M, N, K, a_t, b_t):
+    """With a workspace the plain GEMM cuts the tiles of its last, mostly idle round along K: they are accumulated in
+    parts that a follow-up kernel adds in a fixed order.  Same product as the whole-tile launch up to fp32 summation
+    order, and reproducible run to run."""
+    from coda_kernels_b200 import _lib
+
+    assert _lib.lib.coda_b200_gemm_workspace_bytes(M, N, K) > 0, "this shape should have its last round cut"
+    gen = torch.Generator().manual_seed(11)
+    A = torch.randn((K, M) if a_t else (M, K), generator=gen).to(torch.bfloat16).to(DEV)
+    B = torch.randn((N, K) if b_t else (K, N), generator=gen).to(torch.bfloat16).to(DEV)
+    Av, Bv = (A.mT if a_t else A), (B.mT if b_t else B)
+    ref = Av.float() @ Bv.float()
+    alpha = torch.tensor([0.5], device=DEV)
+    split = ck.ops.gemm(Av, Bv)                                    # compiled dispatch: offers the workspace
+    split32 = ck.ops.gemm(Av, Bv, out_dtype=torch.float32, alpha=alpha)
+    again = ck.ops.gemm(Av, Bv)
+    whole = torch.empty_like(split)
+    ck.ops._ct_gemm_out(Av, Bv, whole, None, None)                  # ctypes binding: no workspace, whole tiles
+    status_ok(ck)
+    assert torch.equal(split, again), "parts are added in a fixed order"
+    close(split, ref, what="tail-split bf16 out")
+    close(split32, 0.5 * ref, tol=1e-5, what="tail-split fp32 out with alpha")
+    assert eager.max_rel_err(split, whole) <= 1e-2, "cut vs whole tiles: one bf16 rounding of a differently ordered fp32 sum"
+    assert _lib.lib.coda_b200_gemm_workspace_bytes(16384, 4096, 28672) == 0, "62 tail tiles cannot be cut profitably"
+
+
 def test_bad_arguments_raise(ck):
     x = torch.zeros(64, 60, dtype=torch.bfloat16, device=DEV)  # K = 60 is not a multiple of 8
     w = torch.zeros(32, 60, dtype=torch.bfloat16, device=DEV)

@@ -200,3 +200,78 @@ def test_a_stalled_producer_is_reported_by_the_mma_role():
     run([producer(cta, 4, 6, 3, 10**6, stall_after=5), mma(cta, 4, 6, 3, 40), epilogue(cta, 4, 10**6)])
     assert cta.abort == K_ERR_FULL
     assert sum(1 for e in cta.log if isinstance(e, tuple) and e[0] == "mma") == 5
+
+
+# ------------------------------------------------------------------------------------------------ tail-split schedule
+# Host restatement of `plan_tail_split` (coda_kernels_b200/csrc/gemm_host.cuh), `WorkSchedule::next`
+# (csrc/gemm_core.cuh) and the slab arithmetic of `split_finalize_kernel`: every k-block of every tile is done exactly
+# once, whole tiles stay whole, each part of a tail tile has its own workspace slab, and the follow-up kernel reads
+# exactly the slabs the GEMM wrote.
+
+SPLIT_OVERHEAD_KB = 12
+
+
+def plan_tail_split(num_tiles: int, num_kb: int, clusters: int):
+    tail = num_tiles % clusters
+    if tail == 0 or clusters < 2 or num_kb < 16:
+        return tail, 1
+    best, best_cost = 1, num_kb
+    for s in range(2, min(2 * clusters // tail, num_kb // 8, 64) + 1):
+        rounds = -(-(tail * s) // clusters)
+        cost = rounds * -(-num_kb // s) + SPLIT_OVERHEAD_KB
+        if cost < best_cost:
+            best, best_cost = s, cost
+    return tail, (best if best > 1 and best_cost * 100 <= num_kb * 85 else 1)
+
+
+def schedule(cluster: int, clusters: int, num_tiles: int, num_kb: int, tail: int, split: int):
+    """Items (tile, kb0, kb1, slab) of one cluster, as the kernel's roles enumerate them."""
+    split = max(split, 1)
+    tail = tail if split > 1 else 0
+    full = num_tiles - tail
+    items = []
+    for i in range(cluster, full + tail * split, clusters):
+        if i < full:
+            items.append((i, 0, num_kb, -1))
+        else:
+            j = i - full
+            part = j // tail
+            items.append((full + j % tail, part * num_kb // split, (part + 1) * num_kb // split, j))
+    return items
+
+
+@pytest.mark.parametrize("num_tiles,num_kb,clusters", [
+    (48, 256, 74), (224, 256, 74), (448, 256, 74), (1792, 256, 74), (8, 128, 74), (12, 64, 74), (6, 129, 74), (76, 32, 74),
+    (1, 700, 74), (20, 40, 148), (3, 1000, 148), (1, 64, 4),
+])
+def test_tail_split_schedule_covers_every_k_block_once(num_tiles, num_kb, clusters):
+    tail, split = plan_tail_split(num_tiles, num_kb, clusters)
+    assert split > 1, "these shapes leave most clusters idle in their last round"
+    assert tail * split <= 2 * clusters, "the workspace holds two partial tiles per cluster"
+    done, written = {}, {}
+    for c in range(clusters):
+        for tile, kb0, kb1, slab in schedule(c, clusters, num_tiles, num_kb, tail, split):
+            assert 0 <= tile < num_tiles and 0 <= kb0 < kb1 <= num_kb
+            assert (slab < 0) == (tile < num_tiles - tail), "whole tiles stay whole; every tail item is a part"
+            for kb in range(kb0, kb1):
+                assert (tile, kb) not in done
+                done[(tile, kb)] = c
+            if slab >= 0:
+                assert slab < tail * split and slab not in written
+                written[slab] = tile
+    assert len(done) == num_tiles * num_kb
+    # the follow-up kernel adds slabs part * tail + t for tail tile t
+    for t in range(tail):
+        for part in range(split):
+            assert written[part * tail + t] == num_tiles - tail + t
+    # what it buys: the last round, in k-blocks
+    last_round = -(-(tail * split) // clusters) * -(-num_kb // split)
+    assert last_round + SPLIT_OVERHEAD_KB <= 0.85 * num_kb
+
+
+def test_tail_split_is_left_off_when_it_cannot_pay():
+    assert plan_tail_split(1024, 448, 74)[1] == 1   # 62 tail tiles: cutting them in two fills two rounds of half length
+    assert plan_tail_split(60, 512, 74)[1] == 1     # same
+    assert plan_tail_split(148, 256, 74)[1] == 1    # no tail at all
+    assert plan_tail_split(48, 8, 74)[1] == 1       # contraction too short to cut
+    assert schedule(3, 74, 200, 10, 52, 1) == [(3, 0, 10, -1), (77, 0, 10, -1), (151, 0, 10, -1)]
