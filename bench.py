@@ -182,12 +182,20 @@ class ClockSampler:
 class Workload:
     """One operator at its benchmark shape, sharded for ``world`` ranks; inputs live on ``device``."""
 
-    def __init__(self, op: str, rank: int, world: int, device: torch.device, pinned_host: bool, rows: int = 0):
+    def __init__(self, op: str, rank: int, world: int, device: torch.device, pinned_host: bool, rows: int = 0, share_of: int = 0):
         import coda_kernels_b200 as ck
         from coda_kernels_b200 import parallel
         from oracle import inputs
 
-        self.op, self.rank, self.world, self.device, self.ck, self.parallel = op, rank, world, device, ck, parallel
+        self.op, self.device, self.ck, self.parallel = op, device, ck, parallel
+        # `share_of` = W on one GPU: the weights are cut as for rank 0 of W ranks and this process times that share
+        # alone, without any communication (`self.world` stays 1; `self.share` scales the flops that are counted)
+        self.rank, self.world, self.share = rank, world, 1.0
+        if share_of > 1:
+            if world != 1:
+                raise SystemExit("--share-of times one rank's share on one GPU")
+            self.share = 1.0 / share_of
+            rank, world = 0, share_of
         s = dict(SHAPES[op])
         if rows:
             s["M"] = rows  # reduced-row variant of the same workload (profiling captures)
@@ -221,7 +229,7 @@ class Workload:
             }
             self.kernels_per_step = 5  # fused GEMM, qk backward, partial fold, dgrad GEMM, wgrad GEMM
         elif op == "llama3_block":
-            if world != 1:
+            if world != 1 or share_of > 1:
                 raise SystemExit("the fused block benchmark runs on one GPU")
             d = inputs.llama3_block_inputs(s["M"], s["dim"], s["ffn"], s["head_dim"], s["heads"], s["kv_heads"], 1024, s["seq_len"])
             host = {k: d[k] for k in ("x0", "y0", "w0", "w1", "w2", "w_qkv", "wn0", "wn1", "positions", "frequencies", "dx", "dqkv")}
@@ -231,8 +239,8 @@ class Workload:
         self.dev = {k: v.to(device) for k, v in host.items()}
         # End-to-end leg on several GPUs: the replicated activation `x` is uploaded as one row slice per rank and
         # all-gathered over NVLink, so the host bytes summed over ranks do not grow with the number of GPUs.
-        self.rows_lo, self.rows_hi = parallel.shard_bounds(s["M"], rank, world, 1)
-        if world > 1 and op != "llama3_block":
+        self.rows_lo, self.rows_hi = parallel.shard_bounds(s["M"], self.rank, self.world, 1)
+        if self.world > 1 and op != "llama3_block":
             host["x"] = host["x"][self.rows_lo:self.rows_hi].contiguous()
         self.host = {k: (v.pin_memory() if pinned_host else v) for k, v in host.items()}
         self.h2d_bytes = sum(v.numel() * v.element_size() for v in self.host.values())
@@ -567,7 +575,7 @@ def measure_device(b: Bench, wl: Workload, reduce_dx: bool | None = None, with_e
     run_step = replay if replay is not None else step_fn
     b.barrier()
     ms_step, windows, clocks = b.time_windows(run_step, args.steps)
-    flops = algorithmic_flops(wl.op, wl.shape)
+    flops = algorithmic_flops(wl.op, wl.shape) * wl.share
     value = flops / (ms_step * 1e-3) / 1e12
     res = {
         "value": value, "unit": "TFLOP/s", "ms_per_step": ms_step, "windows": len(windows),
@@ -669,9 +677,10 @@ def measure_op(b: Bench, op: str, headline: bool) -> tuple[dict, dict]:
     """Everything reported for one operator, plus (headline, several GPUs) its variant with the dx all-reduce.  The
     headline operator also gets the end-to-end leg."""
     args = b.args
-    wl = Workload(op, b.rank, b.world, b.device, pinned_host=headline and not args.no_e2e, rows=args.rows)
+    wl = Workload(op, b.rank, b.world, b.device, pinned_host=headline and not args.no_e2e, rows=args.rows, share_of=args.share_of)
     res = measure_device(b, wl, with_eager=not args.no_eager)
-    res["workload"] = workload_name(op) + (f" [rows reduced to {args.rows}]" if args.rows else "")
+    res["workload"] = (workload_name(op) + (f" [rows reduced to {args.rows}]" if args.rows else "")
+                       + (f" [rank 0's share of a {args.share_of}-GPU job, alone on one GPU, no communication]" if args.share_of > 1 else ""))
     res["shape"] = dict(wl.shape)
     res["parallelism"] = f"{PARALLELISM[op]}-parallel x{b.world}"
     if b.world > 1:
@@ -718,6 +727,8 @@ def main() -> None:
                     help="measure this operator only (as the headline); default: linear_swiglu as the headline plus the other operators under `ops`")
     ap.add_argument("--cpu-rows", type=int, default=0, help="rows of the CPU-baseline sample (0 = default)")
     ap.add_argument("--rows", type=int, default=0, help="override the number of rows M (small captures under ncu); 0 = benchmark shape")
+    ap.add_argument("--share-of", type=int, default=0, help="on one GPU: time rank 0's share of a job sharded over this many GPUs "
+                    "(weights cut as for that job, no communication); implies --no-e2e and no CPU baseline")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-clocks", action="store_true", help="do not sample nvidia-smi during the timed region")
@@ -725,6 +736,8 @@ def main() -> None:
     ap.add_argument("--no-eager", action="store_true", help="skip the extra per-launch-dispatch timing (value_no_graph)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
+    if args.share_of > 1:
+        args.no_e2e = args.no_cpu_baseline = True
 
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
