@@ -118,6 +118,19 @@ def _noop_fake(*args, **kwargs) -> None:
 def _gemm_out(A: Tensor, B: Tensor, out: Tensor, alpha: Optional[Tensor], C: Optional[Tensor] = None) -> None:
     M, K = A.shape
     N = B.shape[1]
+    if C is None:
+        # a plain product may have its last round cut along K: the library says whether it wants the fp32 workspace
+        ws_bytes = int(lib.coda_b200_gemm_workspace_bytes(M, N, K))
+        ws = torch.empty(ws_bytes // 4, dtype=torch.float32, device=A.device) if ws_bytes > 0 else None
+        check(
+            lib.coda_b200_gemm_ws(
+                A.data_ptr(), A.stride(0), A.stride(1), B.data_ptr(), B.stride(0), B.stride(1), out.data_ptr(), out.stride(0),
+                int(out.dtype == torch.float32), M, N, K, alpha.data_ptr() if alpha is not None else None,
+                ws.data_ptr() if ws is not None else None, ws_bytes, status_word(A.device).data_ptr(), _stream(A),
+            ),
+            "gemm",
+        )
+        return
     check(
         lib.coda_b200_gemm_add(
             A.data_ptr(), A.stride(0), A.stride(1), B.data_ptr(), B.stride(0), B.stride(1),

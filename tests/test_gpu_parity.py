@@ -320,13 +320,17 @@ def test_gemm_tail_split_matches_the_whole_tile_schedule(ck, M, N, K, a_t, b_t):
     Av, Bv = (A.mT if a_t else A), (B.mT if b_t else B)
     ref = Av.float() @ Bv.float()
     alpha = torch.tensor([0.5], device=DEV)
-    split = ck.ops.gemm(Av, Bv)                                    # compiled dispatch: offers the workspace
+    split = ck.ops.gemm(Av, Bv)
     split32 = ck.ops.gemm(Av, Bv, out_dtype=torch.float32, alpha=alpha)
-    again = ck.ops.gemm(Av, Bv)
-    whole = torch.empty_like(split)
-    ck.ops._ct_gemm_out(Av, Bv, whole, None, None)                  # ctypes binding: no workspace, whole tiles
+    again = torch.empty_like(split)
+    ck.ops._ct_gemm_out(Av, Bv, again, None, None)                  # the ctypes binding offers the workspace too
+    assert _lib.lib.coda_b200_set_option(b"split_tail", 0) == 0
+    try:
+        whole = ck.ops.gemm(Av, Bv)                                 # whole tiles only
+    finally:
+        assert _lib.lib.coda_b200_set_option(b"split_tail", 1) == 0
     status_ok(ck)
-    assert torch.equal(split, again), "parts are added in a fixed order"
+    assert torch.equal(split, again), "parts are added in a fixed order, whichever binding launches"
     close(split, ref, what="tail-split bf16 out")
     close(split32, 0.5 * ref, tol=1e-5, what="tail-split fp32 out with alpha")
     assert eager.max_rel_err(split, whole) <= 1e-2, "cut vs whole tiles: one bf16 rounding of a differently ordered fp32 sum"
