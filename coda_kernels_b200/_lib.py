@@ -120,8 +120,32 @@ def check(rc: int, what: str) -> None:
         post_call_hook(what)
 
 
+_option_values: dict[str, int] = {}
+
+
 def set_option(name: str, value: int) -> None:
     check(lib.coda_b200_set_option(name.encode(), int(value)), f"set_option({name})")
+    _option_values[name] = int(value)
+
+
+class option_override:
+    """``with option_override("max_ctas", 128): ...`` sets a library option for the launches issued inside the block and
+    puts the previous value (as set through this module; the library's default otherwise) back afterwards.  Options are
+    process-wide and read once per launch, so this is for the thread that issues the launches."""
+
+    _defaults = {"max_ctas": 0, "group_m": 0, "tile_n": 0, "cta_group": 2, "epi_tma": 1, "split_tail": 1, "probe_ld_kb": 0, "probe_st_kb": 0}
+
+    def __init__(self, name: str, value: int):
+        self.name, self.value = name, int(value)
+
+    def __enter__(self):
+        self.previous = _option_values.get(self.name, self._defaults[self.name])
+        set_option(self.name, self.value)
+        return self
+
+    def __exit__(self, *exc):
+        set_option(self.name, self.previous)
+        return False
 
 
 # CODA_B200_OPTIONS="name=value,name=value": library options applied at import (same names as coda_b200_set_option).

@@ -35,6 +35,30 @@ from torch import Tensor
 # CODA_B200_OVERLAP_DX=0 issues the input-gradient all-reduce synchronously (after it, then the weight-gradient GEMM)
 # instead of letting the two overlap: a switch for measurements.
 OVERLAP_DX_ALLREDUCE = os.environ.get("CODA_B200_OVERLAP_DX", "1") == "1"
+# CTAs the weight-gradient GEMM may use while an all-reduce is in flight beside it.  The GEMM is a persistent kernel of
+# one 224 KB CTA per SM with a static share of the tiles each: an SM that the collective's CTAs hold cannot take one, and
+# the CTA that did not fit starts only when the collective has finished and then still runs its whole share, so an
+# uncapped GEMM ends no earlier than if the two had run one after the other (measured on 8 GPUs, linear_swiglu with the
+# 134 MB all-reduce: 1.50 ms serial, 1.59 ms overlapped with all 148 CTAs or with 132 or 124, 1.34 ms with 116 = 148 minus
+# the collective's 32).  A grid that leaves the collective its SMs keeps every CTA resident, at the price of a GEMM that
+# is 148/116 times longer, which pays when that stretch is shorter than the all-reduce.
+# CODA_B200_OVERLAP_MAX_CTAS: "auto" (default: cap at SMs - 32 when the estimate below says it pays), 0 = never, n = always n.
+_OVERLAP_MAX_CTAS = os.environ.get("CODA_B200_OVERLAP_MAX_CTAS", "auto")
+_COLLECTIVE_CTAS = 32
+_GEMM_FLOPS_PER_S = 1.2e15      # sustained rate of one GPU, for the estimate only
+_ALLREDUCE_BUS_BYTES_PER_S = 7.0e11
+
+
+def overlap_max_ctas(flops: float, allreduce_bytes: int, world: int, sms: int) -> int:
+    """CTA cap for a GEMM of ``flops`` that runs beside an all-reduce of ``allreduce_bytes`` over ``world`` ranks (0 = none)."""
+    if _OVERLAP_MAX_CTAS != "auto":
+        return int(_OVERLAP_MAX_CTAS)
+    capped = sms - _COLLECTIVE_CTAS
+    if capped < sms // 2 or world < 2:
+        return 0
+    gemm_stretch = flops / _GEMM_FLOPS_PER_S * (sms / capped - 1.0)
+    allreduce = allreduce_bytes * 2.0 * (world - 1) / world / _ALLREDUCE_BUS_BYTES_PER_S
+    return capped if gemm_stretch < 0.7 * allreduce else 0
 
 
 def shard_bounds(total: int, rank: int, world: int, multiple: int = 1) -> tuple[int, int]:
@@ -117,7 +141,18 @@ def linear_backward_overlapped(grad_pre: Tensor, x: Tensor, weight_shard: Tensor
             if not OVERLAP_DX_ALLREDUCE:
                 pending.pop().wait()
     if need_dw:
-        dweight = ops.gemm(grad_pre.mT, x, alpha=alpha)
+        cap = 0
+        if dx is not None and pending and OVERLAP_DX_ALLREDUCE and reduce_dx:
+            sms = torch.cuda.get_device_properties(x.device).multi_processor_count if x.is_cuda else 148
+            cap = overlap_max_ctas(2.0 * grad_pre.shape[0] * grad_pre.shape[1] * x.shape[1], dx.numel() * dx.element_size(),
+                                   dist.get_world_size(group), sms)
+        if cap > 0:
+            from ._lib import option_override
+
+            with option_override("max_ctas", cap):
+                dweight = ops.gemm(grad_pre.mT, x, alpha=alpha)
+        else:
+            dweight = ops.gemm(grad_pre.mT, x, alpha=alpha)
     for work in pending:
         work.wait()
     return dx, dweight

@@ -129,6 +129,17 @@ def test_sharded_backward_reduces_dx_and_dgamma_two_ranks(tmp_path):
     assert out.read_text() == "1"
 
 
+def test_overlap_cta_cap_estimate():
+    """The weight-gradient GEMM that runs beside the dx all-reduce gives up the collective's SMs only where the stretch of
+    the GEMM is clearly shorter than the all-reduce (short GEMM, large transfer)."""
+    dx_bytes = 16384 * 4096 * 2
+    assert parallel.overlap_max_ctas(2.0 * 16384 * 3584 * 4096, dx_bytes, 8, 148) == 116   # linear_swiglu, share of 8 GPUs
+    assert parallel.overlap_max_ctas(2.0 * 16384 * 14336 * 4096, dx_bytes, 2, 148) == 0    # share of 2: long GEMM, short transfer
+    assert parallel.overlap_max_ctas(2.0 * 8192 * 16032 * 4096, 8192 * 4096 * 2, 8, 148) == 0  # cross entropy, share of 8
+    assert parallel.overlap_max_ctas(1e9, dx_bytes, 1, 148) == 0
+    assert parallel.overlap_max_ctas(1e9, dx_bytes, 8, 40) == 0, "never below half of the SMs"
+
+
 def test_vocab_parallel_lse_exchange_two_ranks(tmp_path):
     out = tmp_path / "result.txt"
     mp.spawn(_lse_worker, args=(2, _free_port(), str(out)), nprocs=2, join=True)
