@@ -236,6 +236,12 @@ class Workload:
             self.kernels_per_step = 18  # 12 GEMMs, 2 rstd + 1 zdz row reductions, 2 dweight column reductions, rope backward
         else:
             raise ValueError(op)
+        if op != "llama3_block":
+            # a plain GEMM whose last round is cut along K is followed by the kernel that adds the parts: count it
+            from coda_kernels_b200._lib import lib
+
+            n_local, m, k = host["weight"].shape[0], s["M"], s["K"]
+            self.kernels_per_step += sum(1 for shape in ((m, k, n_local), (n_local, k, m)) if lib.coda_b200_gemm_workspace_bytes(*shape) > 0)
         self.dev = {k: v.to(device) for k, v in host.items()}
         # End-to-end leg on several GPUs: the replicated activation `x` is uploaded as one row slice per rank and
         # all-gathered over NVLink, so the host bytes summed over ranks do not grow with the number of GPUs.
