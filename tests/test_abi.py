@@ -102,3 +102,26 @@ def test_ops_refuse_cpu_tensors():
         ck.linear_cross_entropy(x, w, torch.zeros(8, dtype=torch.int64))
     with pytest.raises(AssertionError):
         ck.linear_cross_entropy(x, w, torch.zeros(8, dtype=torch.int32), reduction="none")
+
+
+def test_option_override_restores_the_previous_value():
+    from coda_kernels_b200 import _lib
+
+    _lib.set_option("max_ctas", 0)
+    with _lib.option_override("max_ctas", 116):
+        assert _lib._option_values["max_ctas"] == 116
+        with _lib.option_override("max_ctas", 64):
+            assert _lib._option_values["max_ctas"] == 64
+        assert _lib._option_values["max_ctas"] == 116
+    assert _lib._option_values["max_ctas"] == 0
+    with pytest.raises(_lib.CodaB200Error):
+        with _lib.option_override("max_ctas", -7):
+            pass
+    assert _lib._option_values["max_ctas"] == 0
+    # the workspace query is plain host arithmetic (it may look up the SM count, which needs a GPU; without one the
+    # library falls back to a B200's 148)
+    assert _lib.lib.coda_b200_gemm_workspace_bytes(16384, 64, 4096) == 0, "narrow outputs keep their narrow tiles"
+    assert _lib.lib.coda_b200_gemm_workspace_bytes(3584, 4096, 16384) == 2 * 74 * 256 * 256 * 4, "224 tiles on 74 CTA pairs: two tail tiles to cut"
+    assert _lib.lib.coda_b200_gemm_workspace_bytes(16384, 4096, 28672) == 0, "62 tail tiles cannot be cut profitably"
+    with _lib.option_override("split_tail", 0):
+        assert _lib.lib.coda_b200_gemm_workspace_bytes(3584, 4096, 16384) == 0
