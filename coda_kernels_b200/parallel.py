@@ -40,7 +40,7 @@ OVERLAP_DX_ALLREDUCE = os.environ.get("CODA_B200_OVERLAP_DX", "1") == "1"
 # the CTA that did not fit starts only when the collective has finished and then still runs its whole share, so an
 # uncapped GEMM ends no earlier than if the two had run one after the other (measured on 8 GPUs, linear_swiglu with the
 # 134 MB all-reduce: 1.50 ms serial, 1.59 ms overlapped with all 148 CTAs or with 132 or 124, 1.34 ms with 116 = 148 minus
-# the collective's 32).  A grid that leaves the collective its SMs keeps every CTA resident, at the price of a GEMM that
+# the collective's 32; on 4 GPUs 2.68 serial, 2.69 uncapped, 2.61 with 116).  A grid that leaves the collective its SMs keeps every CTA resident, at the price of a GEMM that
 # is 148/116 times longer, which pays when that stretch is shorter than the all-reduce.
 # CODA_B200_OVERLAP_MAX_CTAS: "auto" (default: cap at SMs - 32 when the estimate below says it pays), 0 = never, n = always n.
 _OVERLAP_MAX_CTAS = os.environ.get("CODA_B200_OVERLAP_MAX_CTAS", "auto")
@@ -58,7 +58,7 @@ def overlap_max_ctas(flops: float, allreduce_bytes: int, world: int, sms: int) -
         return 0
     gemm_stretch = flops / _GEMM_FLOPS_PER_S * (sms / capped - 1.0)
     allreduce = allreduce_bytes * 2.0 * (world - 1) / world / _ALLREDUCE_BUS_BYTES_PER_S
-    return capped if gemm_stretch < 0.7 * allreduce else 0
+    return capped if gemm_stretch < 0.9 * allreduce else 0
 
 
 def shard_bounds(total: int, rank: int, world: int, multiple: int = 1) -> tuple[int, int]:

@@ -134,6 +134,7 @@ def test_overlap_cta_cap_estimate():
     the GEMM is clearly shorter than the all-reduce (short GEMM, large transfer)."""
     dx_bytes = 16384 * 4096 * 2
     assert parallel.overlap_max_ctas(2.0 * 16384 * 3584 * 4096, dx_bytes, 8, 148) == 116   # linear_swiglu, share of 8 GPUs
+    assert parallel.overlap_max_ctas(2.0 * 16384 * 7168 * 4096, dx_bytes, 4, 148) == 116   # share of 4
     assert parallel.overlap_max_ctas(2.0 * 16384 * 14336 * 4096, dx_bytes, 2, 148) == 0    # share of 2: long GEMM, short transfer
     assert parallel.overlap_max_ctas(2.0 * 8192 * 16032 * 4096, 8192 * 4096 * 2, 8, 148) == 0  # cross entropy, share of 8
     assert parallel.overlap_max_ctas(1e9, dx_bytes, 1, 148) == 0
