@@ -673,7 +673,7 @@ def measure_kernel(b: Bench, wl: Workload) -> dict:
     torch.cuda.synchronize()
     k_ms = e0.elapsed_time(e1) / n_k
     achieved = k_flops / (k_ms * 1e-3) / 1e12
-    traffic = NCU_TRAFFIC.get(wl.op) if (b.world == 1 and not b.args.rows) else None
+    traffic = NCU_TRAFFIC.get(wl.op) if (b.world == 1 and not b.args.rows and not b.args.share_of) else None
     return {"bound": "tensor", "kernel": label, "achieved": achieved, "peak": b.peak, "unit": "TFLOP/s", "frac": achieved / b.peak,
             "peak_kind": f"{b.peak_kind} burst bf16 (kernel timed alone)", "ms_per_launch": k_ms, "flops_per_launch": k_flops,
             "traffic": traffic}

@@ -198,9 +198,10 @@ inline int full_clusters(const LaunchOptions& opt, int cta_group) {
 }
 
 // Adds the parts of every tail tile (in part order: the result does not depend on timing), applies alpha, converts
-// and writes the tile to D.  Block (t, b) handles rows 16 b .. 16 b + 15 of tail tile t, one 16-byte group of four columns
-// per thread and pass.
-constexpr int kFinalizeRows = 16;
+// and writes the tile to D.  Block (t, b) handles rows 4 b .. 4 b + 3 of tail tile t, one 16-byte group of four columns per
+// thread (a 256-column tile): small blocks, because a launch has only a handful of tail tiles and each output needs
+// `sk_split` loads from slabs that are far apart.
+constexpr int kFinalizeRows = 4;
 template <typename OutT>
 __global__ void __launch_bounds__(256) split_finalize_kernel(const float* __restrict__ ws, OutT* __restrict__ D, long long ldd,
                                                              GemmShape shape, int first_tail_tile, int tile_m, int bn,
@@ -210,7 +211,6 @@ __global__ void __launch_bounds__(256) split_finalize_kernel(const float* __rest
   const float a = alpha != nullptr ? __ldg(alpha) : 1.0f;
   const int groups = bn / 4;
   const long long slab_stride = static_cast<long long>(tile_m) * bn;  // floats per slab
-#pragma unroll 4
   for (int idx = threadIdx.x; idx < kFinalizeRows * groups; idx += 256) {
     const int r = blockIdx.y * kFinalizeRows + idx / groups, g = idx % groups;
     const int row = tm * tile_m + r, col = tn * bn + g * 4;
@@ -218,6 +218,7 @@ __global__ void __launch_bounds__(256) split_finalize_kernel(const float* __rest
     // part p of tail tile t sits in slab p * sk_tail + t
     const float* src = ws + blockIdx.x * slab_stride + static_cast<long long>(r) * bn + g * 4;
     float4 acc = __ldcs(reinterpret_cast<const float4*>(src));
+#pragma unroll 4
     for (int part = 1; part < shape.sk_split; ++part) {
       const float4 v = __ldcs(reinterpret_cast<const float4*>(src + static_cast<long long>(part) * shape.sk_tail * slab_stride));
       acc.x += v.x;
