@@ -40,25 +40,38 @@ OVERLAP_DX_ALLREDUCE = os.environ.get("CODA_B200_OVERLAP_DX", "1") == "1"
 # the CTA that did not fit starts only when the collective has finished and then still runs its whole share, so an
 # uncapped GEMM ends no earlier than if the two had run one after the other (measured on 8 GPUs, linear_swiglu with the
 # 134 MB all-reduce: 1.50 ms serial, 1.59 ms overlapped with all 148 CTAs or with 132 or 124, 1.34 ms with 116 = 148 minus
-# the collective's 32; on 4 GPUs 2.68 serial, 2.69 uncapped, 2.61 with 116).  A grid that leaves the collective its SMs keeps every CTA resident, at the price of a GEMM that
-# is 148/116 times longer, which pays when that stretch is shorter than the all-reduce.
-# CODA_B200_OVERLAP_MAX_CTAS: "auto" (default: cap at SMs - 32 when the estimate below says it pays), 0 = never, n = always n.
+# the collective's 32; on 4 GPUs 2.68 serial, 2.69 uncapped, 2.61 with 116).  A grid that leaves the collective its SMs
+# keeps every CTA resident, at the price of a GEMM that is 148/116 times longer.  So only as much of the weight gradient
+# as the all-reduce lasts runs capped (its first rows, a launch of its own); the rest runs on all SMs afterwards.
+# CODA_B200_OVERLAP_MAX_CTAS: "auto" (default: the plan below), 0 = never cap, n = cap the whole GEMM at n CTAs.
 _OVERLAP_MAX_CTAS = os.environ.get("CODA_B200_OVERLAP_MAX_CTAS", "auto")
 _COLLECTIVE_CTAS = 32
 _GEMM_FLOPS_PER_S = 1.2e15      # sustained rate of one GPU, for the estimate only
 _ALLREDUCE_BUS_BYTES_PER_S = 7.0e11
+_SPLIT_ROWS = 256               # the capped part ends on a tile boundary
 
 
-def overlap_max_ctas(flops: float, allreduce_bytes: int, world: int, sms: int) -> int:
-    """CTA cap for a GEMM of ``flops`` that runs beside an all-reduce of ``allreduce_bytes`` over ``world`` ranks (0 = none)."""
+def overlap_plan(flops: float, rows: int, allreduce_bytes: int, world: int, sms: int) -> tuple[int, int]:
+    """``(cap, capped_rows)`` for a weight-gradient GEMM of ``flops`` with ``rows`` output rows that starts while an all-reduce
+    of ``allreduce_bytes`` over ``world`` ranks is in flight: its first ``capped_rows`` rows run on ``cap`` CTAs, the rest
+    uncapped.  ``(0, 0)``: no cap at all; ``capped_rows == rows``: one capped launch."""
     if _OVERLAP_MAX_CTAS != "auto":
-        return int(_OVERLAP_MAX_CTAS)
+        cap = int(_OVERLAP_MAX_CTAS)
+        return (cap, rows) if cap > 0 else (0, 0)
     capped = sms - _COLLECTIVE_CTAS
     if capped < sms // 2 or world < 2:
-        return 0
-    gemm_stretch = flops / _GEMM_FLOPS_PER_S * (sms / capped - 1.0)
+        return 0, 0
+    gemm_capped = flops / _GEMM_FLOPS_PER_S * sms / capped  # duration of the whole GEMM on the capped grid
     allreduce = allreduce_bytes * 2.0 * (world - 1) / world / _ALLREDUCE_BUS_BYTES_PER_S
-    return capped if gemm_stretch < 0.9 * allreduce else 0
+    fraction = allreduce / gemm_capped
+    if fraction >= 0.85:
+        return capped, rows
+    if fraction < 0.1:
+        return 0, 0  # a transfer this short is not worth a second launch
+    part = int(round(fraction * rows / _SPLIT_ROWS)) * _SPLIT_ROWS
+    if part < _SPLIT_ROWS or rows - part < _SPLIT_ROWS:
+        return (capped, rows) if fraction >= 0.5 else (0, 0)
+    return capped, part
 
 
 def shard_bounds(total: int, rank: int, world: int, multiple: int = 1) -> tuple[int, int]:
@@ -141,16 +154,24 @@ def linear_backward_overlapped(grad_pre: Tensor, x: Tensor, weight_shard: Tensor
             if not OVERLAP_DX_ALLREDUCE:
                 pending.pop().wait()
     if need_dw:
-        cap = 0
+        cap = part = 0
+        rows = grad_pre.shape[1]
         if dx is not None and pending and OVERLAP_DX_ALLREDUCE and reduce_dx:
             sms = torch.cuda.get_device_properties(x.device).multi_processor_count if x.is_cuda else 148
-            cap = overlap_max_ctas(2.0 * grad_pre.shape[0] * grad_pre.shape[1] * x.shape[1], dx.numel() * dx.element_size(),
-                                   dist.get_world_size(group), sms)
+            cap, part = overlap_plan(2.0 * grad_pre.shape[0] * rows * x.shape[1], rows, dx.numel() * dx.element_size(),
+                                     dist.get_world_size(group), sms)
         if cap > 0:
             from ._lib import option_override
 
-            with option_override("max_ctas", cap):
-                dweight = ops.gemm(grad_pre.mT, x, alpha=alpha)
+            if part >= rows:
+                with option_override("max_ctas", cap):
+                    dweight = ops.gemm(grad_pre.mT, x, alpha=alpha)
+            else:
+                # rows [0, part) beside the collective on the SMs it leaves, rows [part, rows) on all SMs once it is done
+                dweight = torch.empty(rows, x.shape[1], dtype=x.dtype, device=x.device)
+                with option_override("max_ctas", cap):
+                    ops.gemm(grad_pre[:, :part].mT, x, out=dweight[:part], alpha=alpha)
+                ops.gemm(grad_pre[:, part:].mT, x, out=dweight[part:], alpha=alpha)
         else:
             dweight = ops.gemm(grad_pre.mT, x, alpha=alpha)
     for work in pending:

@@ -100,7 +100,11 @@ def _overlap_worker(rank: int, world: int, port: int, result_path: str):
 
         def fake_gemm(A, B, out=None, alpha=None, out_dtype=None, C=None):
             res = A.float() @ B.float()
-            return res * alpha if alpha is not None else res
+            res = res * alpha if alpha is not None else res
+            if out is not None:
+                out.copy_(res)
+                return out
+            return res
 
         real_gemm, ops.gemm = ops.gemm, fake_gemm
         try:
@@ -112,7 +116,16 @@ def _overlap_worker(rank: int, world: int, port: int, result_path: str):
             dx, dw = parallel.linear_backward_overlapped(grad_pre[:, lo:hi], x, weight[lo:hi], True, True, None, True, alpha=alpha,
                                                          also_reduce=dgamma)
             dx_keep, _ = parallel.linear_backward_overlapped(grad_pre[:, lo:hi], x, weight[lo:hi], True, False, None, False)
-            ok = (torch.allclose(dx, 0.5 * grad_pre @ weight, atol=1e-5) and torch.allclose(dw, 0.5 * grad_pre[:, lo:hi].T @ x, atol=1e-5)
+            # the weight gradient in two launches (first rows capped beside the collective, the rest afterwards)
+            real_plan, parallel.overlap_plan = parallel.overlap_plan, (lambda *a: (116, 4))
+            try:
+                _, dw_two = parallel.linear_backward_overlapped(grad_pre[:, lo:hi].bfloat16(), x.bfloat16(), weight[lo:hi].bfloat16(), True, True,
+                                                                None, True)
+            finally:
+                parallel.overlap_plan = real_plan
+            ref_two = grad_pre[:, lo:hi].bfloat16().float().T @ x.bfloat16().float()
+            ok_two = dw_two.shape == ref_two.shape and torch.allclose(dw_two.float(), ref_two, atol=5e-2, rtol=2e-2)
+            ok = ok_two and (torch.allclose(dx, 0.5 * grad_pre @ weight, atol=1e-5) and torch.allclose(dw, 0.5 * grad_pre[:, lo:hi].T @ x, atol=1e-5)
                   and torch.equal(dgamma, torch.full((4,), 3.0)) and torch.allclose(dx_keep, grad_pre[:, lo:hi] @ weight[lo:hi], atol=1e-5))
         finally:
             ops.gemm = real_gemm
@@ -129,16 +142,20 @@ def test_sharded_backward_reduces_dx_and_dgamma_two_ranks(tmp_path):
     assert out.read_text() == "1"
 
 
-def test_overlap_cta_cap_estimate():
-    """The weight-gradient GEMM that runs beside the dx all-reduce gives up the collective's SMs only where the stretch of
-    the GEMM is clearly shorter than the all-reduce (short GEMM, large transfer)."""
+def test_overlap_plan_estimate():
+    """The weight-gradient GEMM that starts beside the dx all-reduce gives up the collective's SMs for about as long as
+    the all-reduce lasts: all of a short GEMM, the first rows of a long one, nothing when the transfer is negligible."""
     dx_bytes = 16384 * 4096 * 2
-    assert parallel.overlap_max_ctas(2.0 * 16384 * 3584 * 4096, dx_bytes, 8, 148) == 116   # linear_swiglu, share of 8 GPUs
-    assert parallel.overlap_max_ctas(2.0 * 16384 * 7168 * 4096, dx_bytes, 4, 148) == 116   # share of 4
-    assert parallel.overlap_max_ctas(2.0 * 16384 * 14336 * 4096, dx_bytes, 2, 148) == 0    # share of 2: long GEMM, short transfer
-    assert parallel.overlap_max_ctas(2.0 * 8192 * 16032 * 4096, 8192 * 4096 * 2, 8, 148) == 0  # cross entropy, share of 8
-    assert parallel.overlap_max_ctas(1e9, dx_bytes, 1, 148) == 0
-    assert parallel.overlap_max_ctas(1e9, dx_bytes, 8, 40) == 0, "never below half of the SMs"
+    assert parallel.overlap_plan(2.0 * 16384 * 3584 * 4096, 3584, dx_bytes, 8, 148) == (116, 2304)      # linear_swiglu, share of 8 GPUs
+    assert parallel.overlap_plan(2.0 * 16384 * 768 * 4096, 768, dx_bytes, 8, 148) == (116, 768)        # qknorm_rope, share of 8: all of it
+    cap, part = parallel.overlap_plan(2.0 * 16384 * 7168 * 4096, 7168, dx_bytes, 4, 148)               # share of 4: the first rows only
+    assert cap == 116 and 0 < part < 7168 // 2 and part % 256 == 0
+    assert parallel.overlap_plan(2.0 * 16384 * 14336 * 4096, 14336, dx_bytes, 2, 148) == (0, 0)        # share of 2: a tenth of the GEMM
+    cap, part = parallel.overlap_plan(2.0 * 8192 * 16032 * 4096, 16032, 8192 * 4096 * 2, 8, 148)        # cross entropy, share of 8
+    assert cap == 116 and 2048 <= part <= 4096 and part % 256 == 0
+    assert parallel.overlap_plan(1e9, 1024, dx_bytes, 1, 148) == (0, 0)
+    assert parallel.overlap_plan(1e9, 1024, dx_bytes, 8, 40) == (0, 0), "never below half of the SMs"
+    assert parallel.overlap_plan(2.0 * 16384 * 14336 * 4096, 14336, 1 << 20, 8, 148) == (0, 0), "a 1 MB transfer is not worth a launch"
 
 
 def test_vocab_parallel_lse_exchange_two_ranks(tmp_path):
