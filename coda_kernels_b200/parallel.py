@@ -49,6 +49,9 @@ _COLLECTIVE_CTAS = 32
 _GEMM_FLOPS_PER_S = 1.2e15      # sustained rate of one GPU, for the estimate only
 _ALLREDUCE_BUS_BYTES_PER_S = 7.0e11
 _SPLIT_ROWS = 256               # the capped part ends on a tile boundary
+# CODA_B200_OVERLAP_SPLIT=1: cap only the first rows of a long weight gradient (a launch of its own) instead of all or
+# nothing.  Off by default: the all-or-nothing plan is the one with 4- and 8-GPU measurements behind it.
+_OVERLAP_SPLIT = os.environ.get("CODA_B200_OVERLAP_SPLIT", "0") == "1"
 
 
 def overlap_plan(flops: float, rows: int, allreduce_bytes: int, world: int, sms: int) -> tuple[int, int]:
@@ -64,6 +67,9 @@ def overlap_plan(flops: float, rows: int, allreduce_bytes: int, world: int, sms:
     gemm_capped = flops / _GEMM_FLOPS_PER_S * sms / capped  # duration of the whole GEMM on the capped grid
     allreduce = allreduce_bytes * 2.0 * (world - 1) / world / _ALLREDUCE_BUS_BYTES_PER_S
     fraction = allreduce / gemm_capped
+    if not _OVERLAP_SPLIT:
+        # all or nothing: cap when the 148/116 stretch of the whole GEMM is shorter than the transfer
+        return (capped, rows) if gemm_capped * (1.0 - capped / sms) < 0.9 * allreduce else (0, 0)
     if fraction >= 0.85:
         return capped, rows
     if fraction < 0.1:

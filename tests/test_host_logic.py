@@ -142,19 +142,27 @@ def test_sharded_backward_reduces_dx_and_dgamma_two_ranks(tmp_path):
     assert out.read_text() == "1"
 
 
-def test_overlap_plan_estimate():
-    """The weight-gradient GEMM that starts beside the dx all-reduce gives up the collective's SMs for about as long as
-    the all-reduce lasts: all of a short GEMM, the first rows of a long one, nothing when the transfer is negligible."""
+def test_overlap_plan_estimate(monkeypatch):
+    """The weight-gradient GEMM that starts beside the dx all-reduce gives up the collective's SMs where that costs less than
+    the transfer lasts (default: all of the GEMM or nothing); with the split switched on, only its first rows do."""
     dx_bytes = 16384 * 4096 * 2
-    assert parallel.overlap_plan(2.0 * 16384 * 3584 * 4096, 3584, dx_bytes, 8, 148) == (116, 2304)      # linear_swiglu, share of 8 GPUs
-    assert parallel.overlap_plan(2.0 * 16384 * 768 * 4096, 768, dx_bytes, 8, 148) == (116, 768)        # qknorm_rope, share of 8: all of it
-    cap, part = parallel.overlap_plan(2.0 * 16384 * 7168 * 4096, 7168, dx_bytes, 4, 148)               # share of 4: the first rows only
-    assert cap == 116 and 0 < part < 7168 // 2 and part % 256 == 0
-    assert parallel.overlap_plan(2.0 * 16384 * 14336 * 4096, 14336, dx_bytes, 2, 148) == (0, 0)        # share of 2: a tenth of the GEMM
-    cap, part = parallel.overlap_plan(2.0 * 8192 * 16032 * 4096, 16032, 8192 * 4096 * 2, 8, 148)        # cross entropy, share of 8
-    assert cap == 116 and 2048 <= part <= 4096 and part % 256 == 0
+    swiglu8 = (2.0 * 16384 * 3584 * 4096, 3584, dx_bytes, 8, 148)
+    swiglu4 = (2.0 * 16384 * 7168 * 4096, 7168, dx_bytes, 4, 148)
+    swiglu2 = (2.0 * 16384 * 14336 * 4096, 14336, dx_bytes, 2, 148)
+    ce8 = (2.0 * 8192 * 16032 * 4096, 16032, 8192 * 4096 * 2, 8, 148)
+    monkeypatch.setattr(parallel, "_OVERLAP_SPLIT", False)
+    assert parallel.overlap_plan(*swiglu8) == (116, 3584) and parallel.overlap_plan(*swiglu4) == (116, 7168)
+    assert parallel.overlap_plan(*swiglu2) == (0, 0) and parallel.overlap_plan(*ce8) == (0, 0)
     assert parallel.overlap_plan(1e9, 1024, dx_bytes, 1, 148) == (0, 0)
     assert parallel.overlap_plan(1e9, 1024, dx_bytes, 8, 40) == (0, 0), "never below half of the SMs"
+    monkeypatch.setattr(parallel, "_OVERLAP_SPLIT", True)
+    assert parallel.overlap_plan(*swiglu8) == (116, 2304)
+    assert parallel.overlap_plan(2.0 * 16384 * 768 * 4096, 768, dx_bytes, 8, 148) == (116, 768)   # qknorm_rope, share of 8: all of it
+    cap, part = parallel.overlap_plan(*swiglu4)
+    assert cap == 116 and 0 < part < 7168 // 2 and part % 256 == 0
+    assert parallel.overlap_plan(*swiglu2) == (0, 0)                                            # a tenth of the GEMM: no second launch
+    cap, part = parallel.overlap_plan(*ce8)
+    assert cap == 116 and 2048 <= part <= 4096 and part % 256 == 0
     assert parallel.overlap_plan(2.0 * 16384 * 14336 * 4096, 14336, 1 << 20, 8, 148) == (0, 0), "a 1 MB transfer is not worth a launch"
 
 
